@@ -1,0 +1,430 @@
+// C-ABI layer: argument validation, host<->device staging, kernel selection and
+// error reporting for the entry points declared in include/accera_b200.h.
+//
+// The reference leaves all of this to its loader: a generated GPU host function
+// only launches (docs/Tutorials/GPU/Hello_MatMul_GPU.md:143-158) and hatlib copies
+// numpy buffers to and from the device around it.  Here one call does both jobs:
+// host pointers are staged through a cached per-device workspace (and the call
+// is synchronous), device pointers are used in place on the selected stream.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "accb_internal.h"
+
+namespace accb {
+
+static std::atomic<int64_t> g_launches{0};
+void note_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+thread_local std::string t_error;
+thread_local int t_device = -1;             // -1: use the current CUDA device
+thread_local cudaStream_t t_stream = nullptr;
+
+int fail(int code, const std::string& msg)
+{
+    t_error = msg;
+    return code;
+}
+
+int fail_cuda(const char* what, cudaError_t e)
+{
+    (void)cudaGetLastError();
+    return fail(ACCB_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+// Per-device state: status words written by kernels, a cached staging workspace
+// for host-pointer calls and a scratch buffer for multi-pass kernels.
+struct DeviceState {
+    std::mutex mu;
+    bool ready = false;
+    int num_sms = 0;
+    int* status = nullptr;          // device, kStatusWords ints
+    int* status_host = nullptr;     // pinned mirror
+    void* slot[4] = { nullptr, nullptr, nullptr, nullptr };   // staging: A/data, B/indices, C/output, bias
+    size_t slot_bytes[4] = { 0, 0, 0, 0 };
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+};
+DeviceState g_dev[kMaxDevices];
+
+int current_device(int* dev)
+{
+    if (t_device >= 0) {
+        cudaError_t e = cudaSetDevice(t_device);
+        if (e != cudaSuccess) return fail_cuda("cudaSetDevice", e);
+        *dev = t_device;
+        return ACCB_OK;
+    }
+    cudaError_t e = cudaGetDevice(dev);
+    if (e != cudaSuccess) return fail_cuda("no usable CUDA device (cudaGetDevice)", e);
+    return ACCB_OK;
+}
+
+int device_state(DeviceState** out, int* dev_out)
+{
+    int dev = 0;
+    int rc = current_device(&dev);
+    if (rc != ACCB_OK) return rc;
+    if (dev < 0 || dev >= kMaxDevices) return fail(ACCB_ERR_ARG, "device index out of range");
+    DeviceState& s = g_dev[dev];
+    std::lock_guard<std::mutex> lock(s.mu);
+    if (!s.ready) {
+        cudaDeviceProp prop;
+        cudaError_t e = cudaGetDeviceProperties(&prop, dev);
+        if (e != cudaSuccess) return fail_cuda("cudaGetDeviceProperties", e);
+        if (prop.major != 10) {
+            char buf[160];
+            snprintf(buf, sizeof buf, "device %d is sm_%d%d; this library contains sm_100a code only", dev, prop.major, prop.minor);
+            return fail(ACCB_ERR_CUDA, buf);
+        }
+        s.num_sms = prop.multiProcessorCount;
+        e = cudaMalloc(&s.status, kStatusWords * sizeof(int));
+        if (e != cudaSuccess) return fail_cuda("cudaMalloc(status)", e);
+        e = cudaMemset(s.status, 0, kStatusWords * sizeof(int));
+        if (e != cudaSuccess) return fail_cuda("cudaMemset(status)", e);
+        e = cudaMallocHost(&s.status_host, kStatusWords * sizeof(int));
+        if (e != cudaSuccess) return fail_cuda("cudaMallocHost(status)", e);
+        s.ready = true;
+    }
+    *out = &s;
+    if (dev_out) *dev_out = dev;
+    return ACCB_OK;
+}
+
+bool is_device_pointer(const void* p)
+{
+    if (!p) return false;
+    cudaPointerAttributes a;
+    cudaError_t e = cudaPointerGetAttributes(&a, p);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return false; }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+int ensure(void** buf, size_t* have, size_t need)
+{
+    if (need <= *have) return ACCB_OK;
+    if (*buf) { cudaFree(*buf); *buf = nullptr; *have = 0; }
+    size_t want = need + need / 8;   // a little slack so that slowly growing sizes do not reallocate every call
+    cudaError_t e = cudaMalloc(buf, want);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        e = cudaMalloc(buf, need);
+        want = need;
+    }
+    if (e != cudaSuccess) return fail_cuda("cudaMalloc(staging workspace)", e);
+    *have = want;
+    return ACCB_OK;
+}
+
+// Reads the status words back (synchronises `stream`), clears them, and turns
+// them into an error code.
+int collect_status(DeviceState& s, cudaStream_t stream)
+{
+    cudaError_t e = cudaMemcpyAsync(s.status_host, s.status, kStatusWords * sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail_cuda("kernel execution", e);
+    int w[kStatusWords];
+    memcpy(w, s.status_host, sizeof w);
+    if (w[0] == 0 && w[1] == 0) return ACCB_OK;
+    e = cudaMemsetAsync(s.status, 0, kStatusWords * sizeof(int), stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail_cuda("cudaMemsetAsync(status)", e);
+    char buf[200];
+    if (w[1] != 0) {
+        static const char* sites[] = { "?", "producer waiting for a free stage", "MMA waiting for operands",
+                                       "MMA waiting for a free accumulator", "epilogue waiting for the accumulator" };
+        const int site = (w[1] >> 24) & 0xff;
+        snprintf(buf, sizeof buf, "tcgen05 GEMM: bounded wait ran out (%s, block %d, step %d); results are invalid",
+                 site >= 1 && site <= 4 ? sites[site] : sites[0], w[1] & 0xffffff, w[2]);
+        return fail(ACCB_ERR_TIMEOUT, buf);
+    }
+    snprintf(buf, sizeof buf, "gather: %d index value(s) outside the data dimension; those elements were zero-filled", w[0]);
+    return fail(ACCB_ERR_INDEX, buf);
+}
+
+size_t type_bytes(int t)
+{
+    switch (t) {
+    case ACCB_F32: case ACCB_S32: return 4;
+    case ACCB_F16: case ACCB_BF16: return 2;
+    case ACCB_S8: case ACCB_U8: return 1;
+    default: return 0;
+    }
+}
+
+// Number of elements spanned by a 2-D array with the given strides (0 if empty).
+int64_t span_elems(int64_t d0, int64_t d1, const int64_t* st)
+{
+    if (d0 <= 0 || d1 <= 0) return 0;
+    return (d0 - 1) * st[0] + (d1 - 1) * st[1] + 1;
+}
+
+}  // namespace
+}  // namespace accb
+
+using namespace accb;
+
+extern "C" {
+
+int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c, const float* bias)
+{
+    t_error.clear();
+    if (!desc) return fail(ACCB_ERR_ARG, "accb_gemm: null descriptor");
+    const accb_gemm_desc& d = *desc;
+    if (d.m < 0 || d.n < 0 || d.k < 0) return fail(ACCB_ERR_ARG, "accb_gemm: negative dimension");
+    const size_t ea = type_bytes(d.a_type), eb = type_bytes(d.b_type), ec = type_bytes(d.c_type);
+    if (!ea || !eb || !ec) return fail(ACCB_ERR_ARG, "accb_gemm: unknown element type");
+    for (int i = 0; i < 2; ++i)
+        if (d.a_stride[i] < 1 || d.b_stride[i] < 1 || d.c_stride[i] < 1)
+            return fail(ACCB_ERR_ARG, "accb_gemm: strides must be positive");
+    if (d.epilogue != ACCB_EPI_NONE && d.epilogue != ACCB_EPI_RELU) return fail(ACCB_ERR_ARG, "accb_gemm: unknown epilogue");
+    if (d.compute < ACCB_COMPUTE_AUTO || d.compute > ACCB_COMPUTE_TENSOR_2SM) return fail(ACCB_ERR_ARG, "accb_gemm: unknown compute mode");
+    if (d.m == 0 || d.n == 0) return ACCB_OK;
+    if (!a || !b || !c) return fail(ACCB_ERR_ARG, "accb_gemm: null array pointer");
+
+    DeviceState* sp = nullptr;
+    int dev = 0;
+    int rc = device_state(&sp, &dev);
+    if (rc != ACCB_OK) return rc;
+    DeviceState& s = *sp;
+
+    const bool dev_a = is_device_pointer(a), dev_b = is_device_pointer(b), dev_c = is_device_pointer(c);
+    const bool dev_bias = bias ? is_device_pointer(bias) : dev_c;
+    const bool all_dev = dev_a && dev_b && dev_c && dev_bias;
+    const bool all_host = !dev_a && !dev_b && !dev_c && (bias ? !dev_bias : true);
+    if (!all_dev && !all_host) return fail(ACCB_ERR_ARG, "accb_gemm: mix of host and device pointers");
+
+    GemmLaunch g;
+    g.d = d;
+    g.stream = t_stream;
+    g.status = s.status;
+    g.device = dev;
+    g.num_sms = s.num_sms;
+
+    const size_t bytes_a = (size_t)span_elems(d.m, d.k, d.a_stride) * ea;
+    const size_t bytes_b = (size_t)span_elems(d.k, d.n, d.b_stride) * eb;
+    const size_t bytes_c = (size_t)span_elems(d.m, d.n, d.c_stride) * ec;
+
+    std::unique_lock<std::mutex> lock(s.mu, std::defer_lock);
+    if (all_host) {
+        lock.lock();   // the staging workspace is shared by all host-pointer calls on this device
+        if ((rc = ensure(&s.slot[0], &s.slot_bytes[0], bytes_a)) != ACCB_OK) return rc;
+        if ((rc = ensure(&s.slot[1], &s.slot_bytes[1], bytes_b)) != ACCB_OK) return rc;
+        if ((rc = ensure(&s.slot[2], &s.slot_bytes[2], bytes_c)) != ACCB_OK) return rc;
+        if (bias && (rc = ensure(&s.slot[3], &s.slot_bytes[3], (size_t)d.n * 4)) != ACCB_OK) return rc;
+        cudaError_t e = cudaSuccess;
+        if (bytes_a) e = cudaMemcpyAsync(s.slot[0], a, bytes_a, cudaMemcpyHostToDevice, g.stream);
+        if (e == cudaSuccess && bytes_b) e = cudaMemcpyAsync(s.slot[1], b, bytes_b, cudaMemcpyHostToDevice, g.stream);
+        if (e == cudaSuccess && d.beta != 0.0f) e = cudaMemcpyAsync(s.slot[2], c, bytes_c, cudaMemcpyHostToDevice, g.stream);
+        if (e == cudaSuccess && bias) e = cudaMemcpyAsync(s.slot[3], bias, (size_t)d.n * 4, cudaMemcpyHostToDevice, g.stream);
+        if (e != cudaSuccess) return fail_cuda("host to device copy", e);
+        g.a = s.slot[0]; g.b = s.slot[1]; g.c = s.slot[2]; g.bias = bias ? (const float*)s.slot[3] : nullptr;
+    } else {
+        g.a = a; g.b = b; g.c = c; g.bias = bias;
+    }
+
+    const char* err = "";
+    int n;
+    if (d.k == 0) {
+        // nothing to accumulate: the SIMT kernel applies the epilogue to beta * C
+        n = launch_gemm_simt(g, &err);
+    } else if (d.compute == ACCB_COMPUTE_SIMT) {
+        n = launch_gemm_simt(g, &err);
+    } else if (d.compute == ACCB_COMPUTE_TENSOR || d.compute == ACCB_COMPUTE_TENSOR_2SM) {
+        n = launch_gemm_umma(g, d.compute == ACCB_COMPUTE_TENSOR_2SM, &err);
+    } else {
+        // AUTO: fp32 inputs stay on the bit-faithful fp32 path; narrower inputs take the
+        // tensor cores when the layout allows it and the SIMT kernel otherwise
+        const char* why = nullptr;
+        if (d.a_type != ACCB_F32 && gemm_umma_supported(g, &why)) n = launch_gemm_umma(g, false, &err);
+        else n = launch_gemm_simt(g, &err);
+    }
+    if (n < 0) return fail(n, std::string("accb_gemm: ") + err);
+
+    if (all_host) {
+        cudaError_t e = cudaMemcpyAsync(c, s.slot[2], bytes_c, cudaMemcpyDeviceToHost, g.stream);
+        if (e != cudaSuccess) return fail_cuda("device to host copy", e);
+        return collect_status(s, g.stream);
+    }
+    return ACCB_OK;
+}
+
+int accb_reduce_mean_rank3_dims(int64_t d0, int64_t d1, int64_t d2, int32_t axes_mask, int32_t keepdims, int64_t* out_dims)
+{
+    if (!out_dims) return fail(ACCB_ERR_ARG, "accb_reduce_mean_rank3_dims: null out_dims");
+    axes_mask &= 7;
+    if (axes_mask == 0) axes_mask = 7;
+    const int64_t dims[3] = { d0, d1, d2 };
+    int n = 0;
+    for (int d = 0; d < 3; ++d) {
+        if (axes_mask & (1 << d)) { if (keepdims) out_dims[n++] = 1; }
+        else out_dims[n++] = dims[d];
+    }
+    if (n == 0) out_dims[n++] = 1;
+    return n;
+}
+
+int accb_reduce_mean_rank3(const float* data, int64_t d0, int64_t d1, int64_t d2, float* reduced, int32_t axes_mask)
+{
+    t_error.clear();
+    if (d0 < 0 || d1 < 0 || d2 < 0) return fail(ACCB_ERR_ARG, "accb_reduce_mean_rank3: negative dimension");
+    if (axes_mask < 0 || axes_mask > 7) return fail(ACCB_ERR_ARG, "accb_reduce_mean_rank3: axes_mask must be in [0, 7]");
+    if (axes_mask == 0) axes_mask = 7;
+    const int64_t dims[3] = { d0, d1, d2 };
+    int64_t n_out = 1, n_in = d0 * d1 * d2;
+    for (int d = 0; d < 3; ++d) if (!(axes_mask & (1 << d))) n_out *= dims[d];
+    if (n_out == 0) return ACCB_OK;
+    if (n_in == 0) return fail(ACCB_ERR_ARG, "accb_reduce_mean_rank3: mean over zero elements");
+    if (!data || !reduced) return fail(ACCB_ERR_ARG, "accb_reduce_mean_rank3: null array pointer");
+
+    DeviceState* sp = nullptr;
+    int rc = device_state(&sp, nullptr);
+    if (rc != ACCB_OK) return rc;
+    DeviceState& s = *sp;
+    const bool dev_in = is_device_pointer(data), dev_out = is_device_pointer(reduced);
+    if (dev_in != dev_out) return fail(ACCB_ERR_ARG, "accb_reduce_mean_rank3: mix of host and device pointers");
+    cudaStream_t stream = t_stream;
+
+    std::lock_guard<std::mutex> lock(s.mu);   // staging and scratch buffers are shared per device
+    const float* din = data;
+    float* dout = reduced;
+    if (!dev_in) {
+        if ((rc = ensure(&s.slot[0], &s.slot_bytes[0], (size_t)n_in * 4)) != ACCB_OK) return rc;
+        if ((rc = ensure(&s.slot[2], &s.slot_bytes[2], (size_t)n_out * 4)) != ACCB_OK) return rc;
+        cudaError_t e = cudaMemcpyAsync(s.slot[0], data, (size_t)n_in * 4, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return fail_cuda("host to device copy", e);
+        din = (const float*)s.slot[0];
+        dout = (float*)s.slot[2];
+    }
+    const size_t need = reduce_mean_scratch_bytes(d0, d1, d2, axes_mask, s.num_sms);
+    if (need && (rc = ensure(&s.scratch, &s.scratch_bytes, need)) != ACCB_OK) return rc;
+    const char* err = "";
+    int n = launch_reduce_mean(din, d0, d1, d2, dout, axes_mask, (float*)s.scratch, s.scratch_bytes, s.num_sms, stream, &err);
+    if (n < 0) return fail(n, std::string("accb_reduce_mean_rank3: ") + err);
+    if (!dev_in) {
+        cudaError_t e = cudaMemcpyAsync(reduced, dout, (size_t)n_out * 4, cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return fail_cuda("device to host copy", e);
+    }
+    return ACCB_OK;
+}
+
+int accb_gather_rank2_dims(int64_t d0, int64_t d1, int64_t i0, int64_t i1, int32_t axis, int64_t* out_dims)
+{
+    if (!out_dims) return fail(ACCB_ERR_ARG, "accb_gather_rank2_dims: null out_dims");
+    if (axis == 0) { out_dims[0] = i0; out_dims[1] = i1; out_dims[2] = d1; }
+    else if (axis == 1) { out_dims[0] = d0; out_dims[1] = i0; out_dims[2] = i1; }
+    else return fail(ACCB_ERR_ARG, "accb_gather_rank2_dims: axis must be 0 or 1");
+    return ACCB_OK;
+}
+
+int accb_gather_rank2(const void* data, int64_t d0, int64_t d1, const int64_t* indices, int64_t i0, int64_t i1,
+                      void* output, int32_t axis, int32_t elem_bytes)
+{
+    t_error.clear();
+    if (d0 < 0 || d1 < 0 || i0 < 0 || i1 < 0) return fail(ACCB_ERR_ARG, "accb_gather_rank2: negative dimension");
+    if (axis != 0 && axis != 1) return fail(ACCB_ERR_ARG, "accb_gather_rank2: axis must be 0 or 1");
+    if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4 && elem_bytes != 8)
+        return fail(ACCB_ERR_ARG, "accb_gather_rank2: elem_bytes must be 1, 2, 4 or 8");
+    const int64_t n_idx = i0 * i1;
+    const int64_t n_out = (axis == 0) ? n_idx * d1 : d0 * n_idx;
+    if (n_out == 0) return ACCB_OK;
+    if (!data || !indices || !output) return fail(ACCB_ERR_ARG, "accb_gather_rank2: null array pointer");
+
+    DeviceState* sp = nullptr;
+    int rc = device_state(&sp, nullptr);
+    if (rc != ACCB_OK) return rc;
+    DeviceState& s = *sp;
+    const bool dd = is_device_pointer(data), di = is_device_pointer(indices), dout = is_device_pointer(output);
+    if (dd != di || dd != dout) return fail(ACCB_ERR_ARG, "accb_gather_rank2: mix of host and device pointers");
+    cudaStream_t stream = t_stream;
+    const char* err = "";
+    if (dd) {
+        int n = launch_gather(data, d0, d1, indices, i0, i1, output, axis, elem_bytes, s.status, stream, &err);
+        if (n < 0) return fail(n, std::string("accb_gather_rank2: ") + err);
+        return ACCB_OK;
+    }
+    std::lock_guard<std::mutex> lock(s.mu);
+    const size_t bytes_data = (size_t)(d0 * d1) * elem_bytes, bytes_idx = (size_t)n_idx * 8, bytes_out = (size_t)n_out * elem_bytes;
+    if ((rc = ensure(&s.slot[0], &s.slot_bytes[0], bytes_data)) != ACCB_OK) return rc;
+    if ((rc = ensure(&s.slot[1], &s.slot_bytes[1], bytes_idx)) != ACCB_OK) return rc;
+    if ((rc = ensure(&s.slot[2], &s.slot_bytes[2], bytes_out)) != ACCB_OK) return rc;
+    cudaError_t e = cudaMemcpyAsync(s.slot[0], data, bytes_data, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(s.slot[1], indices, bytes_idx, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return fail_cuda("host to device copy", e);
+    int n = launch_gather(s.slot[0], d0, d1, (const int64_t*)s.slot[1], i0, i1, s.slot[2], axis, elem_bytes, s.status, stream, &err);
+    if (n < 0) return fail(n, std::string("accb_gather_rank2: ") + err);
+    e = cudaMemcpyAsync(output, s.slot[2], bytes_out, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return fail_cuda("device to host copy", e);
+    return collect_status(s, stream);
+}
+
+int accb_set_device(int32_t device)
+{
+    t_error.clear();
+    if (device < 0 || device >= kMaxDevices) return fail(ACCB_ERR_ARG, "accb_set_device: device index out of range");
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return fail_cuda("cudaSetDevice", e);
+    t_device = device;
+    return ACCB_OK;
+}
+
+int accb_set_stream(void* cuda_stream)
+{
+    t_stream = (cudaStream_t)cuda_stream;
+    return ACCB_OK;
+}
+
+int accb_synchronize(void)
+{
+    t_error.clear();
+    DeviceState* sp = nullptr;
+    int rc = device_state(&sp, nullptr);
+    if (rc != ACCB_OK) return rc;
+    std::lock_guard<std::mutex> lock(sp->mu);
+    return collect_status(*sp, t_stream);
+}
+
+const char* accb_last_error(void) { return t_error.c_str(); }
+
+int64_t accb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int accb_release_workspace(void)
+{
+    t_error.clear();
+    int dev = 0;
+    int rc = current_device(&dev);
+    if (rc != ACCB_OK) return rc;
+    DeviceState& s = g_dev[dev];
+    std::lock_guard<std::mutex> lock(s.mu);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail_cuda("cudaDeviceSynchronize", e);
+    for (int i = 0; i < 4; ++i) {
+        if (s.slot[i]) cudaFree(s.slot[i]);
+        s.slot[i] = nullptr;
+        s.slot_bytes[i] = 0;
+    }
+    if (s.scratch) cudaFree(s.scratch);
+    s.scratch = nullptr;
+    s.scratch_bytes = 0;
+    return ACCB_OK;
+}
+
+int accb_device_count(void)
+{
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    return n;
+}
+
+const char* accb_version(void) { return "accera_b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

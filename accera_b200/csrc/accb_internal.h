@@ -1,0 +1,55 @@
+// Internal interfaces between the C-ABI layer (abi.cu) and the kernel files.
+// Everything here takes DEVICE pointers and a stream; host staging, argument
+// validation and error reporting live in abi.cu.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/accera_b200.h"
+
+namespace accb {
+
+// Words of the per-device status buffer that kernels write to (never trap):
+//   [0] gather: number of indices found outside [0, dim)
+//   [1] tcgen05 GEMM: first bounded wait that ran out, encoded as
+//       (site << 24) | (blockIdx.x & 0xffffff), 0 if none
+//   [2] tcgen05 GEMM: k-block / tile the wait was at
+//   [3] reserved
+constexpr int kStatusWords = 4;
+
+struct GemmLaunch {
+    accb_gemm_desc d;
+    const void* a;
+    const void* b;
+    void* c;
+    const float* bias;
+    cudaStream_t stream;
+    int* status;       // device pointer to kStatusWords ints
+    int device;
+    int num_sms;
+};
+
+// gemm_simt.cu: any supported type combination, any strides. Returns launches made (<0: ACCB_ERR_*).
+int launch_gemm_simt(const GemmLaunch& g, const char** err);
+
+// gemm_umma.cu: tcgen05/TMEM path. `supported` explains in *why when it returns false.
+bool gemm_umma_supported(const GemmLaunch& g, const char** why);
+int launch_gemm_umma(const GemmLaunch& g, bool two_sm, const char** err);
+
+// reduce_mean.cu
+// Scratch (fp32 partial sums) a launch needs for these dims, in bytes; 0 when the
+// single-pass kernels are used.
+size_t reduce_mean_scratch_bytes(int64_t d0, int64_t d1, int64_t d2, int axes_mask, int num_sms);
+int launch_reduce_mean(const float* data, int64_t d0, int64_t d1, int64_t d2, float* reduced, int axes_mask,
+                       float* scratch, size_t scratch_bytes, int num_sms, cudaStream_t stream, const char** err);
+
+// gather.cu
+int launch_gather(const void* data, int64_t d0, int64_t d1, const int64_t* indices, int64_t i0, int64_t i1,
+                  void* output, int axis, int elem_bytes, int* status, cudaStream_t stream, const char** err);
+
+// counts kernels launched (reported by accb_launch_count)
+void note_launches(int n);
+
+}  // namespace accb

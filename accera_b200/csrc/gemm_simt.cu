@@ -1,0 +1,235 @@
+// CUDA-core (SIMT) GEMM with the fused epilogue, for sm_100a.
+//
+//   C <- epi(alpha * (A @ B) + beta * C + bias)
+//
+// This is the bit-faithful fp32 path (true fp32 FMA, no TF32) and the general
+// path for every element-type / layout combination the tensor-core kernel does
+// not take: f32, f16, bf16 inputs with an fp32 accumulator, s8/u8 inputs with an
+// int32 accumulator, arbitrary element strides (row- or column-major operands).
+//
+// It replaces the generated per-thread kernel of the reference
+// (docs/Tutorials/GPU/Hello_MatMul_GPU.md:161-191: one thread per C element, C
+// read-modify-written in global memory every k) by a shared-memory tiled kernel:
+// BM x BN output tile per block, BK-deep k tiles double buffered in shared
+// memory with the next tile prefetched into registers, TM x TN register tile per
+// thread, the epilogue applied once to the register tile before the only store.
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+
+#include <type_traits>
+
+#include "accb_internal.h"
+
+namespace accb {
+namespace {
+
+struct SimtParams {
+    int64_t m, n, k;
+    int64_t as0, as1, bs0, bs1, cs0, cs1;
+    float alpha, beta;
+    int relu;
+};
+
+template <typename ACC, typename T>
+__device__ __forceinline__ ACC widen(T v);
+template <> __device__ __forceinline__ float widen<float, float>(float v) { return v; }
+template <> __device__ __forceinline__ float widen<float, __half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float widen<float, __nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ int widen<int, int8_t>(int8_t v) { return (int)v; }
+template <> __device__ __forceinline__ int widen<int, uint8_t>(uint8_t v) { return (int)v; }
+
+template <typename T>
+__device__ __forceinline__ T narrow(float v);
+template <> __device__ __forceinline__ float narrow<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half narrow<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 narrow<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename TA, typename TB, typename TC, typename ACC, int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_simt_kernel(const TA* __restrict__ A, const TB* __restrict__ B, TC* __restrict__ C,
+                 const float* __restrict__ bias, SimtParams p)
+{
+    constexpr int NT = (BM / TM) * (BN / TN);
+    constexpr int LA = (BM * BK) / NT;
+    constexpr int LB = (BN * BK) / NT;
+    static_assert((BM * BK) % NT == 0 && (BN * BK) % NT == 0, "tile must divide evenly over the threads");
+    constexpr int PAD = 4;
+
+    __shared__ ACC As[2][BK][BM + PAD];
+    __shared__ ACC Bs[2][BK][BN + PAD];
+
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN);
+    const int ty = tid / (BN / TN);
+    const int64_t m0 = (int64_t)blockIdx.y * BM;
+    const int64_t n0 = (int64_t)blockIdx.x * BN;
+
+    // Walk the tile along whichever dimension is contiguous in global memory so
+    // that consecutive threads read consecutive addresses.
+    const bool a_kfast = (p.as1 == 1);
+    const bool b_kfast = (p.bs0 == 1);
+
+    ACC ra[LA], rb[LB];
+
+    auto fetch = [&](int64_t k0) {
+#pragma unroll
+        for (int l = 0; l < LA; ++l) {
+            int e = tid + l * NT;
+            int mm = a_kfast ? e / BK : e % BM;
+            int kk = a_kfast ? e % BK : e / BM;
+            int64_t gm = m0 + mm, gk = k0 + kk;
+            ra[l] = (gm < p.m && gk < p.k) ? widen<ACC, TA>(A[gm * p.as0 + gk * p.as1]) : ACC(0);
+        }
+#pragma unroll
+        for (int l = 0; l < LB; ++l) {
+            int e = tid + l * NT;
+            int nn = b_kfast ? e / BK : e % BN;
+            int kk = b_kfast ? e % BK : e / BN;
+            int64_t gn = n0 + nn, gk = k0 + kk;
+            rb[l] = (gn < p.n && gk < p.k) ? widen<ACC, TB>(B[gk * p.bs0 + gn * p.bs1]) : ACC(0);
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int l = 0; l < LA; ++l) {
+            int e = tid + l * NT;
+            int mm = a_kfast ? e / BK : e % BM;
+            int kk = a_kfast ? e % BK : e / BM;
+            As[buf][kk][mm] = ra[l];
+        }
+#pragma unroll
+        for (int l = 0; l < LB; ++l) {
+            int e = tid + l * NT;
+            int nn = b_kfast ? e / BK : e % BN;
+            int kk = b_kfast ? e % BK : e / BN;
+            Bs[buf][kk][nn] = rb[l];
+        }
+    };
+
+    ACC acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = ACC(0);
+
+    const int64_t kt_count = (p.k + BK - 1) / BK;
+    if (kt_count > 0) {
+        fetch(0);
+        stash(0);
+    }
+    __syncthreads();
+
+    for (int64_t kt = 0; kt < kt_count; ++kt) {
+        const int buf = (int)(kt & 1);
+        const bool more = (kt + 1 < kt_count);
+        if (more) fetch((kt + 1) * BK);
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            ACC av[TM], bv[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) av[i] = As[buf][kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) bv[j] = Bs[buf][kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] += av[i] * bv[j];
+        }
+        if (more) stash(buf ^ 1);
+        __syncthreads();
+    }
+
+    // fused epilogue: one read of C (if beta != 0), one write
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int64_t gm = m0 + ty * TM + i;
+        if (gm >= p.m) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int64_t gn = n0 + tx * TN + j;
+            if (gn >= p.n) continue;
+            TC* dst = C + gm * p.cs0 + gn * p.cs1;
+            if constexpr (std::is_same<ACC, int>::value) {
+                int v = acc[i][j];
+                if (p.beta != 0.0f) v += (int)(*dst);
+                if (p.relu && v < 0) v = 0;
+                *dst = (TC)v;
+            } else {
+                float v = (float)acc[i][j];
+                if (p.alpha == 1.0f) {
+                    if (p.beta == 1.0f) v += to_float<TC>(*dst);
+                    else if (p.beta != 0.0f) v += p.beta * to_float<TC>(*dst);
+                } else {
+                    v *= p.alpha;
+                    if (p.beta != 0.0f) v += p.beta * to_float<TC>(*dst);
+                }
+                if (bias) v += bias[gn];
+                if (p.relu) v = fmaxf(v, 0.0f);
+                *dst = narrow<TC>(v);
+            }
+        }
+    }
+}
+
+template <typename TA, typename TB, typename TC, typename ACC>
+cudaError_t launch_typed(const GemmLaunch& g, const SimtParams& p)
+{
+    const int64_t tiles64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
+    if (tiles64 >= 2 * (int64_t)g.num_sms) {
+        constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+        dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)((p.m + BM - 1) / BM));
+        gemm_simt_kernel<TA, TB, TC, ACC, BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, g.stream>>>(
+            (const TA*)g.a, (const TB*)g.b, (TC*)g.c, g.bias, p);
+    } else {
+        // small problems: smaller tiles so that the grid still covers the SMs
+        constexpr int BM = 32, BN = 64, BK = 16, TM = 2, TN = 4;
+        dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)((p.m + BM - 1) / BM));
+        gemm_simt_kernel<TA, TB, TC, ACC, BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, g.stream>>>(
+            (const TA*)g.a, (const TB*)g.b, (TC*)g.c, g.bias, p);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+int launch_gemm_simt(const GemmLaunch& g, const char** err)
+{
+    const accb_gemm_desc& d = g.d;
+    SimtParams p;
+    p.m = d.m; p.n = d.n; p.k = d.k;
+    p.as0 = d.a_stride[0]; p.as1 = d.a_stride[1];
+    p.bs0 = d.b_stride[0]; p.bs1 = d.b_stride[1];
+    p.cs0 = d.c_stride[0]; p.cs1 = d.c_stride[1];
+    p.alpha = d.alpha; p.beta = d.beta; p.relu = (d.epilogue == ACCB_EPI_RELU);
+    if (d.m == 0 || d.n == 0) return 0;
+    if ((d.m + 31) / 32 > 65535) { *err = "SIMT GEMM: M too large for this kernel's grid"; return ACCB_ERR_ARG; }
+
+    cudaError_t e;
+    const int a = d.a_type, b = d.b_type, c = d.c_type;
+    if (a == ACCB_F32 && b == ACCB_F32 && c == ACCB_F32) e = launch_typed<float, float, float, float>(g, p);
+    else if (a == ACCB_F16 && b == ACCB_F16 && c == ACCB_F32) e = launch_typed<__half, __half, float, float>(g, p);
+    else if (a == ACCB_F16 && b == ACCB_F16 && c == ACCB_F16) e = launch_typed<__half, __half, __half, float>(g, p);
+    else if (a == ACCB_BF16 && b == ACCB_BF16 && c == ACCB_F32) e = launch_typed<__nv_bfloat16, __nv_bfloat16, float, float>(g, p);
+    else if (a == ACCB_BF16 && b == ACCB_BF16 && c == ACCB_BF16) e = launch_typed<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, float>(g, p);
+    else if (a == ACCB_S8 && b == ACCB_S8 && c == ACCB_S32) {
+        if (d.alpha != 1.0f || (d.beta != 0.0f && d.beta != 1.0f) || g.bias) { *err = "integer GEMM supports alpha=1, beta in {0,1}, no bias"; return ACCB_ERR_ARG; }
+        e = launch_typed<int8_t, int8_t, int32_t, int>(g, p);
+    } else if (a == ACCB_U8 && b == ACCB_U8 && c == ACCB_S32) {
+        if (d.alpha != 1.0f || (d.beta != 0.0f && d.beta != 1.0f) || g.bias) { *err = "integer GEMM supports alpha=1, beta in {0,1}, no bias"; return ACCB_ERR_ARG; }
+        e = launch_typed<uint8_t, uint8_t, int32_t, int>(g, p);
+    } else {
+        *err = "unsupported GEMM element-type combination";
+        return ACCB_ERR_ARG;
+    }
+    if (e != cudaSuccess) { *err = cudaGetErrorString(e); return ACCB_ERR_CUDA; }
+    note_launches(1);
+    return 1;
+}
+
+}  // namespace accb

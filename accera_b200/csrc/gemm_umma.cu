@@ -1,0 +1,701 @@
+// Tensor-core GEMM with the fused epilogue for sm_100a: tcgen05.mma with TMEM
+// accumulators, operands staged in shared memory by TMA, warp-specialised and
+// persistent.
+//
+//   C <- epi(alpha * (A @ B) + beta * C + bias)
+//     f16 / bf16 inputs -> fp32 accumulate -> f32 | f16 | bf16 output   (kind::f16)
+//     f32 inputs computed as TF32 -> fp32 accumulate -> f32 output      (kind::tf32)
+//     s8 / u8 inputs -> int32 accumulate -> s32 output, exact           (kind::i8)
+//
+// It replaces what the reference generates from its tensorization and caching
+// passes (accera/transforms/src/exec/ExecutionPlanToAffineLoweringPass.cpp:
+// 5986-6533 and 2663-2883): per-warp wmma fragments fed by cooperative
+// global->shared copies with __syncthreads.  The fused epilogue corresponds to the
+// reference's fragment ops applied before store_matrix_sync
+// (accera/acc-translate/src/Target/Cpp/CppPrinterUtils.h:630-655), applied here
+// once per output tile after the whole K accumulation.
+//
+// Layout contract: A is K-contiguous (row-major M x K) and B is K-contiguous
+// (column-major K x N): both are "K-major" operands, loaded without transposition.
+//
+// Kernel structure (one CTA per SM, 192 threads, or CTA pairs with cta_group::2):
+//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of a
+//               128-byte-wide K slab of A (128 rows) and B (256 rows, or 128 per CTA
+//               of a pair) into a ring of shared-memory stages (128B swizzle)
+//   warp 1      allocates TMEM; one lane issues tcgen05.mma (M=128|256, N=256,
+//               K=32 bytes per instruction), commits to the stage's "empty"
+//               mbarrier, and after the last K slab to the accumulator's "full" one
+//   warps 2..5  epilogue: tcgen05.ld the 128 x 256 accumulator (each warp its own 32
+//               TMEM lanes), scale / add C / bias / ReLU / convert, 16-byte stores
+// Two TMEM accumulators (2 x 256 columns) let the epilogue of tile i overlap the
+// main loop of tile i+1.  Tiles are visited in groups of rows so that the CTAs
+// running at the same time share A and B panels in L2.
+//
+// Every mbarrier wait is bounded: when a wait runs out the kernel records where
+// in the status buffer, all roles leave their loops, TMEM is freed and the kernel
+// returns; the host reports ACCB_ERR_TIMEOUT.  Nothing traps.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+
+#include <type_traits>
+
+#include "accb_internal.h"
+
+namespace accb {
+namespace {
+
+constexpr int kBlockM = 128;          // accumulator rows per CTA (TMEM lanes)
+constexpr int kBlockN = 256;          // accumulator columns per tile (UMMA N)
+constexpr int kSlabBytes = 128;       // bytes of K per stage row: one 128B swizzle atom
+constexpr int kMmaKBytes = 32;        // bytes of K one tcgen05.mma consumes
+constexpr int kThreads = 192;
+constexpr int kEpiWarps = 4;
+constexpr int kTmemCols = 512;        // two accumulators of 256 fp32 columns
+constexpr uint32_t kPeerMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address (rank 0 of a pair)
+
+enum { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2 };
+
+// where a bounded wait gave up (status word 1, bits 31..24)
+enum { SITE_PRODUCER_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_TMEM_EMPTY = 3, SITE_EPI_TMEM_FULL = 4 };
+
+template <bool TWO_SM> struct SmemPlan {
+    static constexpr int kABytes = kBlockM * kSlabBytes;                          // 16 KB
+    static constexpr int kBBytes = (TWO_SM ? kBlockN / 2 : kBlockN) * kSlabBytes; // 16 or 32 KB
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = TWO_SM ? 6 : 4;
+    static constexpr int kBarrierBytes = 256;
+    static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;   // +1024: manual alignment
+};
+
+struct UmmaParams {
+    int64_t m, n, k;
+    int64_t cs0, cs1;       // C strides in elements
+    float alpha, beta;
+    int relu;
+    uint32_t idesc;         // tcgen05 instruction descriptor
+    int elem_bytes;         // bytes per A/B element
+    int tiles_m, tiles_n;   // tiles_m counts units of 128 rows (1 CTA) or 256 rows (pair)
+    int group_m;            // tile rows visited together (L2 reuse)
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// arrive on a barrier addressed in the cluster window (own CTA or the pair's rank 0)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
+// Bounded wait.  Returns false when it gave up (after about a second, or as soon
+// as any CTA of the grid has recorded a failure), having recorded the site.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* status, int site, int detail)
+{
+    const long long t0 = clock64();
+    for (uint32_t spin = 0;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 0xff) == 0xff) {
+            if (*(volatile int*)(status + 1) != 0) return false;   // someone else already failed
+            if (clock64() - t0 > 2000000000LL) {
+                if (atomicCAS(status + 1, 0, (site << 24) | (int)(blockIdx.x & 0xffffff)) == 0) status[2] = detail;
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int site, int detail)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, status, site, detail);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+// CTA-pair form: the transaction bytes are signalled on the barrier of the pair's rank-0 CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & kPeerMask), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes
+// with the 128-byte swizzle (what TMA writes): 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);        // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                            // leading byte offset (unused with swizzle): 1
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                            // layout: 128-byte swizzle
+    return d;
+}
+
+template <int KIND, bool TWO_SM>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    if constexpr (!TWO_SM) {
+        if constexpr (KIND == KIND_F16)
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+        else if constexpr (KIND == KIND_TF32)
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+        else
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        if constexpr (KIND == KIND_F16)
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+        else if constexpr (KIND == KIND_TF32)
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+        else
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                         "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+
+// Make `bar` (same offset in every CTA of cta_mask) complete once all tcgen05.mma
+// issued so far by this thread have finished reading shared memory / writing TMEM.
+template <bool TWO_SM>
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    if constexpr (!TWO_SM) {
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    } else {
+        const uint16_t mask = 3;
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                     ::"r"(bar), "h"(mask) : "memory");
+    }
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// tile index -> (tile row, tile column): groups of `group_m` tile rows, rows fastest inside a group
+__device__ __forceinline__ void tile_coords(int t, const UmmaParams& p, int& tm, int& tn)
+{
+    const int group_size = p.group_m * p.tiles_n;
+    const int group = t / group_size;
+    const int first_m = group * p.group_m;
+    const int rows = min(p.tiles_m - first_m, p.group_m);
+    const int in = t - group * group_size;
+    tm = first_m + in % rows;
+    tn = in / rows;
+}
+
+template <typename TC> struct OutVec;   // 32 consecutive output elements of one row
+
+template <typename TC, typename ACC>
+__device__ __forceinline__ void epilogue_row(const uint32_t (&acc)[32], TC* __restrict__ crow, int64_t col0, int ncols,
+                                             bool vec_ok, int64_t cs1, const float* __restrict__ bias,
+                                             const UmmaParams& p)
+{
+    // crow points at C[row, 0]; this thread owns columns [col0, col0 + 32) of which ncols are inside the matrix
+    if constexpr (std::is_same<ACC, int>::value) {
+        int v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (int)acc[j];
+        if (vec_ok && ncols == 32) {
+            int4* dst = reinterpret_cast<int4*>(crow + col0);
+            if (p.beta != 0.0f) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    int4 o = dst[q];
+                    v[4 * q] += o.x; v[4 * q + 1] += o.y; v[4 * q + 2] += o.z; v[4 * q + 3] += o.w;
+                }
+            }
+            if (p.relu) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = max(v[j], 0);
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) dst[q] = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (j < ncols) {
+                    TC* d = crow + (col0 + j) * cs1;
+                    int x = v[j];
+                    if (p.beta != 0.0f) x += (int)*d;
+                    if (p.relu) x = max(x, 0);
+                    *d = (TC)x;
+                }
+            }
+        }
+    } else {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
+        if (p.alpha != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+        }
+        if (vec_ok && ncols == 32) {
+            if constexpr (std::is_same<TC, float>::value) {
+                float4* dst = reinterpret_cast<float4*>(crow + col0);
+                if (p.beta != 0.0f) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        float4 o = dst[q];
+                        v[4 * q] += p.beta * o.x; v[4 * q + 1] += p.beta * o.y;
+                        v[4 * q + 2] += p.beta * o.z; v[4 * q + 3] += p.beta * o.w;
+                    }
+                }
+                if (bias) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += __ldg(bias + col0 + j);
+                }
+                if (p.relu) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+                // 16-bit outputs: 8 elements per 16-byte vector
+                uint4* dst = reinterpret_cast<uint4*>(crow + col0);
+                if (p.beta != 0.0f) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint4 o = dst[q];
+                        const TC* h = reinterpret_cast<const TC*>(&o);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[8 * q + e] += p.beta * (float)h[e];
+                    }
+                }
+                if (bias) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] += __ldg(bias + col0 + j);
+                }
+                if (p.relu) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 o;
+                    TC* h = reinterpret_cast<TC*>(&o);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) h[e] = (TC)v[8 * q + e];
+                    dst[q] = o;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (j < ncols) {
+                    TC* d = crow + (col0 + j) * cs1;
+                    float x = v[j];
+                    if (p.beta != 0.0f) x += p.beta * (float)*d;
+                    if (bias) x += __ldg(bias + col0 + j);
+                    if (p.relu) x = fmaxf(x, 0.0f);
+                    *d = (TC)x;
+                }
+            }
+        }
+    }
+}
+
+template <int KIND, typename TC, bool TWO_SM>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 TC* __restrict__ C, const float* __restrict__ bias, const UmmaParams p)
+{
+    using Plan = SmemPlan<TWO_SM>;
+    using ACC = typename std::conditional<KIND == KIND_I8, int, float>::type;
+    constexpr int S = Plan::kStages;
+    constexpr int kCtas = TWO_SM ? 2 : 1;
+
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: required by the 128B swizzle pattern shared by TMA and the MMA descriptors
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bars = smem_base + S * Plan::kStageBytes;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
+    auto tmem_full_bar = [&](int b) { return bars + 8u * (2 * S + b); };
+    auto tmem_empty_bar = [&](int b) { return bars + 8u * (2 * S + 2 + b); };
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_gen + S * Plan::kStageBytes + 8 * (2 * S + 4));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = TWO_SM ? cluster_ctarank() : 0u;
+    const bool leader = (rank == 0);
+
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full_bar(s), 1);    // the producer's arrive.expect_tx (pair: rank 0's, covering both CTAs' bytes)
+            mbar_init(empty_bar(s), 1);   // one tcgen05.commit
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tmem_full_bar(b), 1);                    // one tcgen05.commit
+            mbar_init(tmem_empty_bar(b), kEpiWarps * kCtas);   // one arrive per epilogue warp (of both CTAs)
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        if constexpr (TWO_SM)
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32((const void*)tmem_holder)), "r"(kTmemCols) : "memory");
+        else
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32((const void*)tmem_holder)), "r"(kTmemCols) : "memory");
+        if constexpr (TWO_SM) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        else asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if constexpr (TWO_SM) cluster_sync_all(); else __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_units = (int)gridDim.x / kCtas;
+    const int unit = (int)blockIdx.x / kCtas;
+    const int slab_elems = kSlabBytes / p.elem_bytes;
+    const int num_kb = (int)((p.k + slab_elems - 1) / slab_elems);
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = unit; t < num_tiles && ok; t += num_units) {
+                int tm, tn;
+                tile_coords(t, p, tm, tn);
+                const int row_a = (tm * kCtas + (int)rank) * kBlockM;
+                const int row_b = tn * kBlockN + (TWO_SM ? (int)rank * (kBlockN / 2) : 0);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, SITE_PRODUCER_EMPTY, kb)) { ok = false; break; }
+                    const uint32_t sa = smem_base + s * Plan::kStageBytes;
+                    const uint32_t sb = sa + Plan::kABytes;
+                    if constexpr (TWO_SM) {
+                        if (leader) mbar_arrive_expect_tx(full_bar(s), 2u * Plan::kStageBytes);
+                        tma_load_2d_pair(sa, &map_a, full_bar(s), kb * slab_elems, row_a);
+                        tma_load_2d_pair(sb, &map_b, full_bar(s), kb * slab_elems, row_b);
+                    } else {
+                        mbar_arrive_expect_tx(full_bar(s), (uint32_t)Plan::kStageBytes);
+                        tma_load_2d(sa, &map_a, full_bar(s), kb * slab_elems, row_a);
+                        tma_load_2d(sb, &map_b, full_bar(s), kb * slab_elems, row_b);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (rank 0 of a pair only) ----------------
+        if (lane == 0 && leader) {
+            uint32_t it = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = unit; t < num_tiles && ok; t += num_units, ++local) {
+                const int buf = local & 1;
+                const uint32_t tph = (local >> 1) & 1u;
+                if (!mbar_wait(tmem_empty_bar(buf), tph ^ 1u, p.status, SITE_MMA_TMEM_EMPTY, local)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kBlockN);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % S;
+                    const uint32_t ph = (it / S) & 1u;
+                    if (!mbar_wait(full_bar(s), ph, p.status, SITE_MMA_FULL, kb)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = smem_base + s * Plan::kStageBytes;
+                    const uint32_t sb = sa + Plan::kABytes;
+                    const uint64_t adesc = make_smem_desc(sa);
+                    const uint64_t bdesc = make_smem_desc(sb);
+#pragma unroll
+                    for (int j = 0; j < kSlabBytes / kMmaKBytes; ++j) {
+                        // advancing K inside the swizzle atom: +32 bytes on the start address (16-byte units)
+                        umma<KIND, TWO_SM>(tmem_d, adesc + (uint64_t)(j * (kMmaKBytes >> 4)),
+                                           bdesc + (uint64_t)(j * (kMmaKBytes >> 4)), p.idesc,
+                                           (kb > 0 || j > 0) ? 1u : 0u);
+                    }
+                    umma_commit<TWO_SM>(empty_bar(s));            // frees the stage once these MMAs have read it
+                }
+                if (ok) umma_commit<TWO_SM>(tmem_full_bar(buf));  // accumulator complete
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int q = warp & 3;                       // TMEM lane quarter this warp may access
+        const bool c_vec = (p.cs1 == 1) && ((p.cs0 * (int64_t)sizeof(TC)) % 16 == 0) &&
+                           ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        int local = 0;
+        bool ok = true;
+        for (int t = unit; t < num_tiles && ok; t += num_units, ++local) {
+            int tm, tn;
+            tile_coords(t, p, tm, tn);
+            const int buf = local & 1;
+            const uint32_t tph = (local >> 1) & 1u;
+            // all 32 lanes must agree before the warp-wide TMEM loads below
+            if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), tph, p.status, SITE_EPI_TMEM_FULL, local))) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int64_t row = (int64_t)(tm * kCtas + (int)rank) * kBlockM + q * 32 + lane;
+            const int64_t col_tile = (int64_t)tn * kBlockN;
+            TC* crow = C + row * p.cs0;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kBlockN);
+#pragma unroll 1
+            for (int c = 0; c < kBlockN / 32; ++c) {
+                uint32_t acc[32];
+                tmem_ld32(taddr + (uint32_t)(c * 32), acc);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int64_t col0 = col_tile + c * 32;
+                if (row < p.m && col0 < p.n) {
+                    const int ncols = (int)min((int64_t)32, p.n - col0);
+                    epilogue_row<TC, ACC>(acc, crow, col0, ncols, c_vec, p.cs1, bias, p);
+                }
+            }
+            // this warp has drained its part of the accumulator: hand it back to the MMA issuer
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(TWO_SM ? (tmem_empty_bar(buf) & kPeerMask) : tmem_empty_bar(buf));
+        }
+    }
+
+    // teardown: every role ends here, also after a bounded wait gave up
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if constexpr (TWO_SM) cluster_sync_all(); else __syncthreads();
+    if (*(volatile int*)(p.status + 1) != 0) {
+        // failure path: give loads that are still in flight time to land before shared memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        if constexpr (TWO_SM) cluster_sync_all(); else __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if constexpr (TWO_SM)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn()
+{
+    // resolved through the runtime so that the library has no link-time dependency on the driver library
+    static EncodeTiledFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return (EncodeTiledFn)f;
+    }();
+    return fn;
+}
+
+int elem_size(int t)
+{
+    switch (t) {
+    case ACCB_F32: case ACCB_S32: return 4;
+    case ACCB_F16: case ACCB_BF16: return 2;
+    default: return 1;
+    }
+}
+
+// K-major operand [rows, k] with `ld` elements between rows; box = 128 bytes of K by box_rows rows
+bool make_operand_map(CUtensorMap* map, const void* base, int type, int64_t rows, int64_t k, int64_t ld, int box_rows)
+{
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return false;
+    CUtensorMapDataType dt;
+    switch (type) {
+    case ACCB_F16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+    case ACCB_BF16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
+    case ACCB_F32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
+    default: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    }
+    const int es = elem_size(type);
+    cuuint64_t dims[2] = { (cuuint64_t)k, (cuuint64_t)rows };
+    cuuint64_t strides[1] = { (cuuint64_t)(ld * es) };
+    cuuint32_t box[2] = { (cuuint32_t)(kSlabBytes / es), (cuuint32_t)box_rows };
+    cuuint32_t estr[2] = { 1, 1 };
+    CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+uint32_t make_idesc(int a_type, int b_type, bool int_acc, bool f16_out_acc, int m, int n)
+{
+    auto fmt = [](int t) -> uint32_t {
+        switch (t) {
+        case ACCB_F16: return 0; case ACCB_BF16: return 1; case ACCB_F32: return 2;   // f16, bf16, tf32
+        case ACCB_S8: return 1; default: return 0;                                    // s8, u8
+        }
+    };
+    uint32_t d = 0;
+    d |= (int_acc ? 2u : (f16_out_acc ? 0u : 1u)) << 4;   // accumulator format: s32 / f16 / f32
+    d |= fmt(a_type) << 7;
+    d |= fmt(b_type) << 10;
+    // bits 13, 14: no negation; bits 15, 16: both operands K-major
+    d |= (uint32_t)(n >> 3) << 17;
+    d |= (uint32_t)(m >> 4) << 24;
+    return d;
+}
+
+template <int KIND, typename TC, bool TWO_SM>
+int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap& mb, UmmaParams p, const char** err)
+{
+    using Plan = SmemPlan<TWO_SM>;
+    auto kernel = gemm_umma_kernel<KIND, TC, TWO_SM>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal);
+    if (e != cudaSuccess) { *err = cudaGetErrorString(e); return ACCB_ERR_CUDA; }
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = Plan::kTotal;
+    cfg.stream = g.stream;
+    cudaLaunchAttribute attr[1];
+    int units = g.num_sms;
+    if (TWO_SM) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        cfg.gridDim = dim3(2 * (unsigned)(g.num_sms / 2));
+        int max_clusters = 0;
+        e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
+        if (e != cudaSuccess || max_clusters < 1) { *err = "tcgen05 GEMM: no CTA pair can be resident"; (void)cudaGetLastError(); return ACCB_ERR_CUDA; }
+        units = max_clusters < g.num_sms / 2 ? max_clusters : g.num_sms / 2;
+    }
+    if (units > num_tiles) units = num_tiles;
+    cfg.gridDim = dim3((unsigned)(units * (TWO_SM ? 2 : 1)));
+    e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, (TC*)g.c, g.bias, p);
+    if (e != cudaSuccess) { *err = cudaGetErrorString(e); return ACCB_ERR_CUDA; }
+    note_launches(1);
+    return 1;
+}
+
+}  // namespace
+
+bool gemm_umma_supported(const GemmLaunch& g, const char** why)
+{
+    const accb_gemm_desc& d = g.d;
+    const int a = d.a_type, b = d.b_type, c = d.c_type;
+    const bool f16_family = (a == ACCB_F16 && b == ACCB_F16 && (c == ACCB_F32 || c == ACCB_F16)) ||
+                            (a == ACCB_BF16 && b == ACCB_BF16 && (c == ACCB_F32 || c == ACCB_BF16));
+    const bool tf32 = (a == ACCB_F32 && b == ACCB_F32 && c == ACCB_F32);
+    const bool i8 = ((a == ACCB_S8 || a == ACCB_U8) && (b == ACCB_S8 || b == ACCB_U8) && c == ACCB_S32);
+    if (!(f16_family || tf32 || i8)) { *why = "element types have no tensor-core path"; return false; }
+    if (i8 && (d.alpha != 1.0f || (d.beta != 0.0f && d.beta != 1.0f) || g.bias)) { *why = "integer GEMM supports alpha=1, beta in {0,1}, no bias"; return false; }
+    if (d.a_stride[1] != 1 || d.b_stride[0] != 1) { *why = "tensor-core path needs K-contiguous A (row-major) and B (column-major)"; return false; }
+    const int es = elem_size(a);
+    if ((d.a_stride[0] * es) % 16 || (d.b_stride[1] * es) % 16) { *why = "operand row pitch must be a multiple of 16 bytes"; return false; }
+    if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15)) { *why = "operand base must be 16-byte aligned"; return false; }
+    if (d.m < 1 || d.n < 1 || d.k < 1) { *why = "empty problem"; return false; }
+    if (d.m > (int64_t)1 << 30 || d.n > (int64_t)1 << 30 || d.k > (int64_t)1 << 30) { *why = "dimension too large"; return false; }
+    if (!encode_tiled_fn()) { *why = "cuTensorMapEncodeTiled is not available"; return false; }
+    return true;
+}
+
+int launch_gemm_umma(const GemmLaunch& g, bool two_sm, const char** err)
+{
+    const accb_gemm_desc& d = g.d;
+    const char* why = nullptr;
+    if (!gemm_umma_supported(g, &why)) { *err = why; return ACCB_ERR_ARG; }
+
+    CUtensorMap ma, mb;
+    const int b_box_rows = two_sm ? kBlockN / 2 : kBlockN;
+    if (!make_operand_map(&ma, g.a, d.a_type, d.m, d.k, d.a_stride[0], kBlockM) ||
+        !make_operand_map(&mb, g.b, d.b_type, d.n, d.k, d.b_stride[1], b_box_rows)) {
+        *err = "tcgen05 GEMM: cuTensorMapEncodeTiled failed";
+        return ACCB_ERR_CUDA;
+    }
+
+    const bool int_acc = (d.c_type == ACCB_S32);
+    UmmaParams p;
+    p.m = d.m; p.n = d.n; p.k = d.k;
+    p.cs0 = d.c_stride[0]; p.cs1 = d.c_stride[1];
+    p.alpha = d.alpha; p.beta = d.beta; p.relu = (d.epilogue == ACCB_EPI_RELU);
+    p.idesc = make_idesc(d.a_type, d.b_type, int_acc, false, two_sm ? 2 * kBlockM : kBlockM, kBlockN);
+    p.elem_bytes = elem_size(d.a_type);
+    const int rows_per_unit = two_sm ? 2 * kBlockM : kBlockM;
+    p.tiles_m = (int)((d.m + rows_per_unit - 1) / rows_per_unit);
+    p.tiles_n = (int)((d.n + kBlockN - 1) / kBlockN);
+    p.group_m = two_sm ? 8 : 16;
+    p.status = g.status;
+    if ((int64_t)p.tiles_m * p.tiles_n > 0x3fffffff) { *err = "tcgen05 GEMM: too many tiles"; return ACCB_ERR_ARG; }
+
+#define ACCB_UMMA_LAUNCH(KIND, TC)                                                          \
+    (two_sm ? launch_variant<KIND, TC, true>(g, ma, mb, p, err) : launch_variant<KIND, TC, false>(g, ma, mb, p, err))
+
+    if (d.a_type == ACCB_F16 || d.a_type == ACCB_BF16) {
+        if (d.c_type == ACCB_F32) return ACCB_UMMA_LAUNCH(KIND_F16, float);
+        if (d.c_type == ACCB_F16) return ACCB_UMMA_LAUNCH(KIND_F16, __half);
+        return ACCB_UMMA_LAUNCH(KIND_F16, __nv_bfloat16);
+    }
+    if (d.a_type == ACCB_F32) return ACCB_UMMA_LAUNCH(KIND_TF32, float);
+    return ACCB_UMMA_LAUNCH(KIND_I8, int32_t);
+#undef ACCB_UMMA_LAUNCH
+}
+
+}  // namespace accb

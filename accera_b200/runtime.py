@@ -1,0 +1,267 @@
+"""ctypes binding of libaccera_b200.so (the C ABI declared in include/accera_b200.h).
+
+This is the Python face of the launch layer that replaces the reference's
+accera/runtime + acc-gpu-runner + hatlib device plumbing for the GEMM(+ReLU),
+reduce_mean and gather functions.  Arrays may be numpy arrays (host memory: the
+library stages them through the GPU and the call is synchronous) or torch CUDA
+tensors (used in place, enqueued on torch's current stream, not synchronised).
+
+There is no CPU fallback: if the library is missing or no B200 is visible every
+compute call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import numpy as np
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libaccera_b200.so")
+
+F32, F16, BF16, S8, S32, U8 = 0, 1, 2, 3, 4, 5
+COMPUTE_AUTO, COMPUTE_SIMT, COMPUTE_TENSOR, COMPUTE_TENSOR_2SM = 0, 1, 2, 3
+EPI_NONE, EPI_RELU = 0, 1
+ERR_ARG, ERR_CUDA, ERR_INDEX, ERR_TIMEOUT, ERR_LIMIT = -1, -2, -3, -4, -5
+
+TYPE_BYTES = {F32: 4, F16: 2, BF16: 2, S8: 1, S32: 4, U8: 1}
+_NP_TYPE = {"float32": F32, "float16": F16, "int8": S8, "int32": S32, "uint8": U8}
+_COMPUTE = {"auto": COMPUTE_AUTO, "simt": COMPUTE_SIMT, "tensor": COMPUTE_TENSOR, "tensor_2sm": COMPUTE_TENSOR_2SM}
+
+EXPORTED_SYMBOLS = (
+    "accb_gemm", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
+    "accb_gather_rank2_dims", "accb_set_device", "accb_set_stream", "accb_synchronize", "accb_last_error",
+    "accb_launch_count", "accb_release_workspace", "accb_device_count", "accb_version",
+)
+
+
+class AccbError(RuntimeError):
+    """A C-ABI entry point returned a negative status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+
+
+class GemmDesc(ctypes.Structure):
+    _fields_ = [
+        ("m", ctypes.c_int64), ("n", ctypes.c_int64), ("k", ctypes.c_int64),
+        ("a_type", ctypes.c_int32), ("b_type", ctypes.c_int32), ("c_type", ctypes.c_int32),
+        ("compute", ctypes.c_int32),
+        ("a_stride", ctypes.c_int64 * 2), ("b_stride", ctypes.c_int64 * 2), ("c_stride", ctypes.c_int64 * 2),
+        ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
+        ("epilogue", ctypes.c_int32), ("reserved", ctypes.c_int32),
+    ]
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the library (building it first when the sources are newer and nvcc is present)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        from . import build as _build
+        _build.build()
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(f"{LIB_PATH} is missing: run `python -m accera_b200.build` (needs nvcc); there is no CPU fallback")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32
+    L.accb_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp]
+    L.accb_gemm.restype = ctypes.c_int
+    L.accb_reduce_mean_rank3.argtypes = [vp, i64, i64, i64, vp, i32]
+    L.accb_reduce_mean_rank3.restype = ctypes.c_int
+    L.accb_reduce_mean_rank3_dims.argtypes = [i64, i64, i64, i32, i32, ctypes.POINTER(i64)]
+    L.accb_reduce_mean_rank3_dims.restype = ctypes.c_int
+    L.accb_gather_rank2.argtypes = [vp, i64, i64, vp, i64, i64, vp, i32, i32]
+    L.accb_gather_rank2.restype = ctypes.c_int
+    L.accb_gather_rank2_dims.argtypes = [i64, i64, i64, i64, i32, ctypes.POINTER(i64)]
+    L.accb_gather_rank2_dims.restype = ctypes.c_int
+    L.accb_set_device.argtypes = [i32]
+    L.accb_set_device.restype = ctypes.c_int
+    L.accb_set_stream.argtypes = [vp]
+    L.accb_set_stream.restype = ctypes.c_int
+    L.accb_synchronize.restype = ctypes.c_int
+    L.accb_last_error.restype = ctypes.c_char_p
+    L.accb_launch_count.restype = ctypes.c_int64
+    L.accb_release_workspace.restype = ctypes.c_int
+    L.accb_device_count.restype = ctypes.c_int
+    L.accb_version.restype = ctypes.c_char_p
+    _lib = L
+    return L
+
+
+def _check(rc: int) -> None:
+    if rc < 0:
+        raise AccbError(rc, lib().accb_last_error().decode())
+
+
+def device_count() -> int:
+    return int(lib().accb_device_count())
+
+
+def launch_count() -> int:
+    return int(lib().accb_launch_count())
+
+
+def set_device(device: int) -> None:
+    _check(lib().accb_set_device(int(device)))
+
+
+def set_stream(stream_handle: int) -> None:
+    _check(lib().accb_set_stream(ctypes.c_void_p(int(stream_handle) or None)))
+
+
+def synchronize() -> None:
+    _check(lib().accb_synchronize())
+
+
+def release_workspace() -> None:
+    _check(lib().accb_release_workspace())
+
+
+# ---------------------------------------------------------------------------
+# array adaptors
+# ---------------------------------------------------------------------------
+
+def _is_torch(x) -> bool:
+    return type(x).__module__.split(".")[0] == "torch"
+
+
+def _describe(x, kind: Optional[str] = None):
+    """-> (pointer, element type code, shape, element strides, is_device)."""
+    if _is_torch(x):
+        import torch
+        tmap = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int8: S8, torch.int32: S32,
+                torch.uint8: U8}
+        if kind is not None:
+            code = {"bfloat16": BF16, "float16": F16, "float32": F32, "int8": S8, "uint8": U8, "int32": S32}[kind]
+        elif x.dtype in tmap:
+            code = tmap[x.dtype]
+        elif x.dtype == torch.int64:
+            code = None
+        else:
+            raise TypeError(f"unsupported tensor dtype {x.dtype}")
+        return x.data_ptr(), code, tuple(x.shape), tuple(x.stride()), x.is_cuda
+    a = x
+    if not isinstance(a, np.ndarray):
+        raise TypeError("expected a numpy array or a torch tensor")
+    if kind == "bfloat16":
+        if a.dtype != np.uint16:
+            raise TypeError("bfloat16 numpy arrays are passed as uint16 bit patterns")
+        code = BF16
+    elif a.dtype == np.int64:
+        code = None
+    else:
+        code = _NP_TYPE.get(str(a.dtype))
+        if code is None:
+            raise TypeError(f"unsupported array dtype {a.dtype}")
+    return a.ctypes.data, code, a.shape, tuple(s // a.itemsize for s in a.strides), False
+
+
+def _raw(x):
+    """-> (pointer, shape, element size) of a dense first-major array of any element type."""
+    if _is_torch(x):
+        if not x.is_contiguous():
+            raise ValueError("expected a contiguous tensor")
+        return x.data_ptr(), tuple(x.shape), x.element_size()
+    if not isinstance(x, np.ndarray):
+        raise TypeError("expected a numpy array or a torch tensor")
+    if not x.flags.c_contiguous:
+        raise ValueError("expected a C-contiguous array")
+    return x.ctypes.data, x.shape, x.itemsize
+
+
+def _sync_torch_stream(*arrays) -> None:
+    """Device-pointer calls run on torch's current stream of the tensors' device."""
+    for x in arrays:
+        if _is_torch(x) and x.is_cuda:
+            import torch
+            set_device(x.device.index)
+            set_stream(torch.cuda.current_stream(x.device).cuda_stream)
+            return
+
+
+# ---------------------------------------------------------------------------
+# the three ops
+# ---------------------------------------------------------------------------
+
+def gemm(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: bool = False, compute: str = "auto",
+         kind: Optional[str] = None, out_kind: Optional[str] = None) -> None:
+    """C <- epi(alpha * A @ B + beta * C + bias), in place in C.
+
+    A [M,K], B [K,N], C [M,N]; strides are taken from the arrays, so a Fortran-
+    ordered B is the reference's LAST_MAJOR layout.  `kind`/`out_kind` = "bfloat16"
+    marks uint16 numpy arrays as bf16 bit patterns.
+    """
+    pa, ta, sha, sta, da = _describe(A, kind)
+    pb, tb, shb, stb, db = _describe(B, kind)
+    pc, tc, shc, stc, dc = _describe(C, out_kind)
+    if len(sha) != 2 or len(shb) != 2 or len(shc) != 2:
+        raise ValueError("gemm operands must be rank 2")
+    m, k = sha
+    k2, n = shb
+    if k2 != k or tuple(shc) != (m, n):
+        raise ValueError(f"shape mismatch: A{sha} B{shb} C{shc}")
+    pbias = None
+    if bias is not None:
+        pbias, tbias, shbias, _, _ = _describe(bias)
+        if tbias != F32 or tuple(shbias) != (n,):
+            raise ValueError("bias must be fp32 of length N")
+    d = GemmDesc()
+    d.m, d.n, d.k = m, n, k
+    d.a_type, d.b_type, d.c_type = ta, tb, tc
+    d.compute = _COMPUTE[compute]
+    d.a_stride[0], d.a_stride[1] = max(sta[0], 1), max(sta[1], 1)
+    d.b_stride[0], d.b_stride[1] = max(stb[0], 1), max(stb[1], 1)
+    d.c_stride[0], d.c_stride[1] = max(stc[0], 1), max(stc[1], 1)
+    d.alpha, d.beta = alpha, beta
+    d.epilogue = EPI_RELU if relu else EPI_NONE
+    _sync_torch_stream(A, B, C)
+    _check(lib().accb_gemm(ctypes.byref(d), pa, pb, pc, pbias))
+
+
+def reduce_mean_rank3_dims(d0: int, d1: int, d2: int, axes, keepdims: int = 1):
+    axes = list(range(3)) if not axes else [a % 3 for a in axes]
+    mask = sum(1 << a for a in set(axes))
+    out = (ctypes.c_int64 * 3)()
+    n = lib().accb_reduce_mean_rank3_dims(d0, d1, d2, mask, int(keepdims), out)
+    _check(n)
+    return tuple(out[i] for i in range(n)), mask
+
+
+def reduce_mean_rank3(data, reduced, axes) -> None:
+    """reduced <- mean of rank-3 fp32 `data` over `axes` (ONNX ReduceMean; empty axes = all)."""
+    pd, td, shd, std_, dd = _describe(data)
+    pr, tr, shr, str_, dr = _describe(reduced)
+    if td != F32 or tr != F32 or len(shd) != 3:
+        raise ValueError("reduce_mean_rank3 takes a rank-3 fp32 array")
+    axes = list(range(3)) if not axes else [a % 3 for a in axes]
+    mask = sum(1 << a for a in set(axes))
+    _sync_torch_stream(data, reduced)
+    _check(lib().accb_reduce_mean_rank3(pd, shd[0], shd[1], shd[2], pr, mask))
+
+
+def gather_rank2(data, indices, output, axis: int = 0) -> None:
+    """output <- gather(data, indices, axis) for rank-2 data and rank-2 int64 indices."""
+    pd, shd, esize = _raw(data)
+    pi, shi, isize = _raw(indices)
+    po, sho, osize = _raw(output)
+    idx_dtype = str(indices.dtype)
+    if "int64" not in idx_dtype:
+        raise TypeError("indices must be int64")
+    if len(shd) != 2 or len(shi) != 2:
+        raise ValueError("gather_rank2 takes rank-2 data and rank-2 indices")
+    if osize != esize:
+        raise TypeError("output element size differs from data element size")
+    _sync_torch_stream(data, indices, output)
+    _check(lib().accb_gather_rank2(pd, shd[0], shd[1], pi, shi[0], shi[1], po, int(axis), int(esize)))
+
+
+def gather_rank2_dims(d0: int, d1: int, i0: int, i1: int, axis: int):
+    out = (ctypes.c_int64 * 3)()
+    _check(lib().accb_gather_rank2_dims(d0, d1, i0, i1, int(axis), out))
+    return tuple(out)

@@ -1,0 +1,141 @@
+/*
+ * accera_b200 - C ABI of the B200 (sm_100a) launch layer behind HAT packages.
+ *
+ * A HAT package built by accera_b200.Package exports, per function, exactly the
+ * prototype the reference compiler would have exported
+ *     void <base_name>_<16 hex>(T_in* A, T_in* B, T_out* C);            (GEMM family)
+ *     void <name>(int64_t dims..., float* out, float* data, int64_t* indices);   (gather)
+ * and each of those thin stubs forwards into one of the entry points declared
+ * here.  Everything is extern "C", plain pointers and sizes, no C++ or torch types.
+ *
+ * Pointers may be host or device addresses.  Host buffers are staged through a
+ * cached device workspace and the call returns after the result is back in host
+ * memory; device buffers are used in place, the kernel is enqueued on the stream
+ * selected with accb_set_stream() and the call returns without synchronising
+ * (like the launcher the reference generates, which only launches).
+ *
+ * Every entry point returns 0 on success or a negative ACCB_ERR_* code; the text
+ * of the last error on the calling thread is available from accb_last_error().
+ * There is no CPU fallback: without a usable CUDA device every compute entry
+ * point fails with ACCB_ERR_CUDA.
+ */
+#ifndef ACCERA_B200_H
+#define ACCERA_B200_H
+
+#if defined(__cplusplus)
+#include <cstdint>
+extern "C" {
+#else
+#include <stdint.h>
+#endif
+
+/* element types (storage) */
+enum {
+    ACCB_F32 = 0,
+    ACCB_F16 = 1,
+    ACCB_BF16 = 2,
+    ACCB_S8 = 3,
+    ACCB_S32 = 4,
+    ACCB_U8 = 5
+};
+
+/* how a GEMM is computed */
+enum {
+    ACCB_COMPUTE_AUTO = 0,   /* tensor cores for f16/bf16/s8/u8 inputs, fp32 SIMT for f32 inputs */
+    ACCB_COMPUTE_SIMT = 1,   /* CUDA-core FMA in fp32 / int32: bit-faithful fp32 */
+    ACCB_COMPUTE_TENSOR = 2, /* tcgen05: f16/bf16 -> f32, s8/u8 -> s32, f32 inputs as TF32 */
+    ACCB_COMPUTE_TENSOR_2SM = 3 /* tcgen05 with CTA pairs (cta_group::2); same numerics as TENSOR */
+};
+
+/* fused epilogue applied to the accumulator before it is stored
+ * (reference: MMAFragmentOp, accera/ir/include/value/ValueMMAOp.h:64-71) */
+enum {
+    ACCB_EPI_NONE = 0,
+    ACCB_EPI_RELU = 1
+};
+
+enum {
+    ACCB_OK = 0,
+    ACCB_ERR_ARG = -1,       /* bad descriptor, null pointer, unsupported combination */
+    ACCB_ERR_CUDA = -2,      /* a CUDA call failed (no device, out of memory, launch error) */
+    ACCB_ERR_INDEX = -3,     /* gather met an index outside [0, dim): that row was zero-filled */
+    ACCB_ERR_TIMEOUT = -4,   /* a bounded device-side wait ran out; results are invalid */
+    ACCB_ERR_LIMIT = -5      /* a fixed-capacity resource is too small for the request */
+};
+
+/*
+ * GEMM with fused epilogue:   C <- epi(alpha * (A @ B) + beta * C + bias[j])
+ *
+ * Replaces the reference's generated GEMM kernels and their launchers
+ * (accera/transforms/src/exec/ExecutionPlanToAffineLoweringPass.cpp:5986-6533,
+ *  accera/acc-translate/src/Target/Cpp/GpuDialectCppPrinter.cpp:426-561); the
+ * nest it implements is README.md:61-76 (C is INPUT_OUTPUT, i.e. beta = 1).
+ * A is M x K, B is K x N, C is M x N; strides are in elements and are the
+ * affine_map of the .hat argument (row-major {ld,1}, column-major {1,ld}).
+ */
+typedef struct accb_gemm_desc {
+    int64_t m, n, k;
+    int32_t a_type, b_type, c_type; /* ACCB_F32 ... */
+    int32_t compute;                /* ACCB_COMPUTE_* */
+    int64_t a_stride[2];
+    int64_t b_stride[2];
+    int64_t c_stride[2];
+    float alpha;
+    float beta;
+    int32_t epilogue;               /* ACCB_EPI_* */
+    int32_t reserved;
+} accb_gemm_desc;
+
+/* bias may be NULL; when given it is n fp32 values added to every row before the ReLU */
+int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c, const float* bias);
+
+/*
+ * ReduceMean over a dense first-major rank-3 fp32 array.
+ * Replaces the nests of kernels/reduce_mean/naive_runtime_sized.py:66-148.
+ * axes_mask bit d set = dimension d is averaged away.  `reduced` holds the kept
+ * dimensions densely, first-major (keepdims only changes the shape reported by
+ * accb_reduce_mean_rank3_dims, not the element order).
+ */
+int accb_reduce_mean_rank3(const float* data, int64_t d0, int64_t d1, int64_t d2, float* reduced, int32_t axes_mask);
+
+/* host-only helper: writes the output dims, returns the output rank (1..3) */
+int accb_reduce_mean_rank3_dims(int64_t d0, int64_t d1, int64_t d2, int32_t axes_mask, int32_t keepdims,
+                                int64_t* out_dims);
+
+/*
+ * Gather with rank-2 data and rank-2 int64 indices, dense first-major.
+ * Replaces the nests of kernels/gather/naive_runtime_sized.py:26-49 and
+ * accera/python/accera/test/dsl_tests.py:1596-1601, 1642-1647.
+ *   axis 0: output[i,j,k] = data[indices[i,j], k]     output is (i0, i1, d1)
+ *   axis 1: output[i,j,k] = data[i, indices[j,k]]     output is (d0, i0, i1)
+ * elem_bytes is 1, 2, 4 or 8; elements are copied bit for bit.  Like the
+ * reference, negative indices are not supported; unlike it, an index outside
+ * [0, dim) is not dereferenced: the element is zero-filled and the call reports
+ * ACCB_ERR_INDEX (host buffers: from this call; device buffers: from the next
+ * accb_synchronize()).
+ */
+int accb_gather_rank2(const void* data, int64_t d0, int64_t d1, const int64_t* indices, int64_t i0, int64_t i1,
+                      void* output, int32_t axis, int32_t elem_bytes);
+
+/* host-only helper: output dims of the gather above */
+int accb_gather_rank2_dims(int64_t d0, int64_t d1, int64_t i0, int64_t i1, int32_t axis, int64_t* out_dims);
+
+/*
+ * Runtime control.  These replace what the reference leaves to its loader
+ * (device selection and synchronisation, tools/benchmarkers/accera_gemm.py:612-626)
+ * and accera/runtime; none of them appears in a HAT prototype.
+ */
+int accb_set_device(int32_t device);      /* device used by this thread's following calls */
+int accb_set_stream(void* cuda_stream);   /* cudaStream_t used for device-pointer calls; NULL = default stream */
+int accb_synchronize(void);               /* wait for the selected stream; reports deferred device-side errors */
+const char* accb_last_error(void);        /* text of the last error on this thread ("" if none) */
+int64_t accb_launch_count(void);          /* kernels launched by this library so far (all threads) */
+int accb_release_workspace(void);         /* free the cached staging buffers of the current device */
+int accb_device_count(void);              /* number of visible CUDA devices, 0 if none / no driver */
+const char* accb_version(void);
+
+#if defined(__cplusplus)
+} /* extern "C" */
+#endif
+
+#endif /* ACCERA_B200_H */
