@@ -224,24 +224,21 @@ def _key(k: str) -> str:
 
 
 def _table(header: str, table: Dict[str, Any]) -> str:
-    """`[header]` with scalar/array keys first, then nested tables as `[header.sub]`."""
-    lines = [f"[{header}]"]
+    """`[header]` with scalar / array / empty-table keys first, then non-empty nested tables as `[header.sub]`.
+    A table that holds nothing but nested tables gets no header of its own (TOML creates it implicitly)."""
+    lines = []
     nested = []
     for k, v in table.items():
-        if isinstance(v, dict) and v and not _all_scalars(v):
-            nested.append((k, v))
-        elif isinstance(v, dict):
+        if isinstance(v, dict) and v:
             nested.append((k, v))
         else:
             lines.append(f"{_key(k)} = {_scalar(v)}")
-    text = "\n".join(lines) + "\n"
+    text = ""
+    if lines or not nested:
+        text = "\n".join([f"[{header}]"] + lines) + "\n"
     for k, v in nested:
-        text += "\n" + _table(f"{header}.{_key(k)}", v)
+        text += ("\n" if text else "") + _table(f"{header}.{_key(k)}", v)
     return text
-
-
-def _all_scalars(d: Dict[str, Any]) -> bool:
-    return all(not isinstance(v, dict) for v in d.values())
 
 
 def _function_table(group: str, f: Function) -> str:

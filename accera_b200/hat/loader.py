@@ -1,0 +1,266 @@
+"""Loads a HAT package and calls / benchmarks its functions, with the call shape of the third-party
+`hatlib` the reference's tests and tools use (it is not part of the reference tree):
+
+    package, functions = load("P.hat")              # verifiers.py:18-38
+    functions.names                                  # verifiers.py:27
+    functions["matmul_relu_<hash>"](A, B, C)         # numpy arrays, mutated in place
+    functions.matmul_relu                            # base-name alias (first function with that base name)
+    run_benchmark("P.hat", batch_size=5, min_time_in_sec=5)   # README.md:136, accera_gemm.py:612-626
+
+Arguments are checked against the descriptor before the call: element type, shape and element strides
+of every affine_array (a column-major B must be passed Fortran-ordered, mfma_tests.py:184-192), element
+count of every runtime_array (evaluated from the dimension arguments).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+import statistics
+import time
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+
+from .hat_file import Function, HATFile, Parameter
+
+_NP_OF_C = {
+    "float": np.float32, "double": np.float64, "float16_t": np.float16, "bfloat16_t": np.uint16,
+    "int8_t": np.int8, "int16_t": np.int16, "int32_t": np.int32, "int64_t": np.int64,
+    "uint8_t": np.uint8, "uint16_t": np.uint16, "uint32_t": np.uint32, "uint64_t": np.uint64, "bool": np.bool_,
+}
+_CTYPES_OF_C = {
+    "int8_t": ctypes.c_int8, "int16_t": ctypes.c_int16, "int32_t": ctypes.c_int32, "int64_t": ctypes.c_int64,
+    "uint8_t": ctypes.c_uint8, "uint16_t": ctypes.c_uint16, "uint32_t": ctypes.c_uint32, "uint64_t": ctypes.c_uint64,
+    "float": ctypes.c_float, "double": ctypes.c_double, "bool": ctypes.c_bool,
+}
+
+
+class HATFunction:
+    """A callable bound to one exported symbol, checked against its descriptor."""
+
+    def __init__(self, desc: Function, symbol):
+        self.desc = desc
+        self.name = desc.name
+        self._symbol = symbol
+        self._symbol.restype = None
+
+    def _marshal(self, args):
+        params = self.desc.arguments
+        if len(args) != len(params):
+            raise ValueError(f"{self.name}: expected {len(params)} arguments, got {len(args)}")
+        values: Dict[str, int] = {}
+        c_args = []
+        keep = []
+        for p, a in zip(params, args):
+            if p.logical_type == "element":
+                ct = _CTYPES_OF_C.get(p.element_type)
+                if ct is None:
+                    raise TypeError(f"{self.name}: unsupported element type {p.element_type}")
+                if p.usage == "input":
+                    values[p.name] = int(a) if "int" in p.element_type else a
+                    c_args.append(ct(a))
+                else:
+                    # output / in-out scalar: pass a 1-element numpy array or a ctypes instance
+                    if isinstance(a, np.ndarray):
+                        if a.dtype != _NP_OF_C[p.element_type] or a.size != 1:
+                            raise TypeError(f"{self.name}: argument {p.name!r} must be a 1-element {p.element_type} array")
+                        c_args.append(ctypes.c_void_p(a.ctypes.data))
+                    else:
+                        c_args.append(ctypes.byref(a))
+                    keep.append(a)
+        # arrays second, once the dimension values are known
+        it = iter(c_args)
+        out = []
+        for p, a in zip(params, args):
+            if p.logical_type == "element":
+                out.append(next(it))
+                continue
+            if not isinstance(a, np.ndarray):
+                raise TypeError(f"{self.name}: argument {p.name!r} must be a numpy array")
+            want = _NP_OF_C.get(p.element_type)
+            if want is None or a.dtype != want:
+                raise TypeError(f"{self.name}: argument {p.name!r} has dtype {a.dtype}, descriptor says {p.element_type}")
+            if p.logical_type == "affine_array":
+                if list(a.shape) != list(p.shape):
+                    raise ValueError(f"{self.name}: argument {p.name!r} has shape {a.shape}, descriptor says {p.shape}")
+                strides = [s // a.itemsize for s in a.strides]
+                for dim, st, ws in zip(a.shape, strides, p.affine_map):
+                    if dim > 1 and st != ws:
+                        raise ValueError(f"{self.name}: argument {p.name!r} has element strides {strides}, descriptor "
+                                         f"says {p.affine_map} (pass column-major arrays with order='F')")
+            else:
+                n = _eval_size(p.size or "", values)
+                if a.size != n or not a.flags.c_contiguous:
+                    raise ValueError(f"{self.name}: argument {p.name!r} must be a dense array of {n} elements ({p.size})")
+            out.append(ctypes.c_void_p(a.ctypes.data))
+        return out, keep
+
+    def __call__(self, *args, device_id: Optional[int] = None):
+        c_args, _keep = self._marshal(args)
+        self._symbol(*c_args)
+
+
+def _eval_size(expr: str, values: Dict[str, int]) -> int:
+    n = 1
+    for tok in filter(None, (t.strip() for t in expr.split("*"))):
+        n *= int(tok) if re.fullmatch(r"\d+", tok) else int(values[tok])
+    return n
+
+
+class FunctionMap:
+    def __init__(self, functions: Dict[str, HATFunction], aliases: Dict[str, str]):
+        self._functions = functions
+        self._aliases = aliases
+
+    @property
+    def names(self) -> List[str]:
+        return list(self._functions)
+
+    def _resolve(self, name: str) -> HATFunction:
+        if name in self._functions:
+            return self._functions[name]
+        if name in self._aliases:
+            return self._functions[self._aliases[name]]
+        raise KeyError(name)
+
+    def __getitem__(self, name: str) -> HATFunction:
+        return self._resolve(name)
+
+    def __getattr__(self, name: str) -> HATFunction:
+        try:
+            return self._resolve(name)
+        except KeyError:
+            raise AttributeError(name) from None
+
+    def __contains__(self, name: str) -> bool:
+        return name in self._functions or name in self._aliases
+
+    def __iter__(self):
+        return iter(self._functions.values())
+
+    def __len__(self):
+        return len(self._functions)
+
+
+class HATPackage:
+    def __init__(self, hat: HATFile, library: ctypes.CDLL):
+        self.hat_file = hat
+        self.library = library
+        self.name = hat.name
+
+    def get_functions(self) -> List[Function]:
+        return list(self.hat_file.functions)
+
+
+def _aliases(hat: HATFile) -> Dict[str, str]:
+    out: Dict[str, str] = {}
+    for m in re.finditer(r"\(\*(\w+)\)\([^)]*\)\s*=\s*(\w+);", hat.declaration_code):
+        out.setdefault(m.group(1), m.group(2))
+    return out
+
+
+def load(hat_path: str, try_dynamic_load: bool = True):
+    """-> (HATPackage, FunctionMap).  The package must be dynamically linked (HAT_DYNAMIC)."""
+    hat = HATFile.read(hat_path)
+    lib_path = hat.link_target_path
+    if not lib_path or not lib_path.endswith((".so", ".dll", ".dylib")):
+        raise RuntimeError(f"{hat_path}: link_target {hat.dependencies.get('link_target')!r} is not a dynamic library; "
+                           "build the package with Format.HAT_DYNAMIC to load it")
+    if not os.path.exists(lib_path):
+        raise FileNotFoundError(lib_path)
+    library = ctypes.CDLL(lib_path)
+    functions: Dict[str, HATFunction] = {}
+    for f in hat.functions:
+        if f.calling_convention == "device":
+            continue
+        functions[f.name] = HATFunction(f, getattr(library, f.name))
+    return HATPackage(hat, library), FunctionMap(functions, _aliases(hat))
+
+
+# ---------------------------------------------------------------------------
+# benchmarking (row fields as printed in docs/Tutorials/GPU/Hello_MatMul_GPU.md:207-209)
+# ---------------------------------------------------------------------------
+
+class BenchmarkResult:
+    def __init__(self, function_name: str, batch_means: List[float]):
+        self.function_name = function_name
+        means = sorted(batch_means)
+        self.mean = statistics.mean(means)
+        self.median_of_means = statistics.median(means)
+        small = means[: max(1, len(means) // 2)]
+        self.mean_of_small_means = statistics.mean(small)
+        trim = len(means) // 5
+        core = means[trim: len(means) - trim] or means
+        self.robust_mean = statistics.mean(core)
+        self.min_of_means = means[0]
+
+    def as_dict(self) -> Dict[str, Any]:
+        return {k: getattr(self, k) for k in ("function_name", "mean", "median_of_means", "mean_of_small_means",
+                                              "robust_mean", "min_of_means")}
+
+    def __repr__(self):
+        return repr(self.as_dict())
+
+
+def generate_arg_values(fn: Function, rng: np.random.Generator, dim_value: int = 128):
+    """Random inputs matching a function's descriptor (dimension arguments get `dim_value`)."""
+    values: Dict[str, int] = {}
+    for p in fn.arguments:
+        if p.logical_type == "element" and p.usage == "input":
+            values[p.name] = dim_value
+    args = []
+    for p in fn.arguments:
+        if p.logical_type == "element":
+            if p.usage == "input":
+                args.append(values[p.name])
+            else:
+                args.append(np.zeros(1, dtype=_NP_OF_C[p.element_type]))
+            continue
+        dt = _NP_OF_C[p.element_type]
+        if p.logical_type == "affine_array":
+            shape = tuple(p.shape)
+            fortran = len(shape) > 1 and p.affine_map[0] == 1 and p.affine_map[-1] != 1
+        else:
+            shape = (_eval_size(p.size or "", values),)
+            fortran = False
+        if p.element_type == "bfloat16_t":
+            a = (rng.standard_normal(shape).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        elif np.issubdtype(dt, np.floating):
+            a = rng.random(shape).astype(dt)
+        elif p.usage == "input" and "index" in p.name.lower() or (p.usage == "input" and dt == np.int64):
+            a = rng.integers(0, dim_value, size=shape).astype(dt)       # valid gather indices
+        else:
+            info = np.iinfo(dt)
+            a = rng.integers(max(info.min, -4), min(info.max, 4), size=shape).astype(dt)
+        args.append(np.asfortranarray(a) if fortran else np.ascontiguousarray(a))
+    return args
+
+
+def run_benchmark(hat_path: str, store_in_hat: bool = False, batch_size: int = 10, min_time_in_sec: float = 10,
+                  input_sets_minimum_size_MB: int = 50, device_id: int = 0, verbose: bool = False,
+                  functions: Optional[List[str]] = None) -> List[BenchmarkResult]:
+    """Times every function of the package: batches of `batch_size` calls until `min_time_in_sec` has
+    elapsed (at least 3 batches), on host arrays, so each call includes the library's host<->device staging."""
+    _, fmap = load(hat_path)
+    rng = np.random.default_rng(0)
+    results = []
+    for fn in fmap:
+        if functions and fn.name not in functions:
+            continue
+        args = generate_arg_values(fn.desc, rng)
+        fn(*args)                                      # warm-up (and first-touch of the staging workspace)
+        batch_means: List[float] = []
+        t_end = time.perf_counter() + float(min_time_in_sec)
+        while len(batch_means) < 3 or time.perf_counter() < t_end:
+            t0 = time.perf_counter()
+            for _ in range(batch_size):
+                fn(*args)
+            batch_means.append((time.perf_counter() - t0) / batch_size)
+            if len(batch_means) >= 100000:
+                break
+        r = BenchmarkResult(fn.name, batch_means)
+        if verbose:
+            print(r.as_dict())
+        results.append(r)
+    return results

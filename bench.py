@@ -1,0 +1,435 @@
+#!/usr/bin/env python
+"""Benchmark of the HAT GEMM(+ReLU) hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
+
+Workload (the configuration the headline metric is quoted on): bf16 GEMM + fused
+ReLU, M=65536, N=8192, K=8192, A ~ N(0,1) row-major split by M-row blocks over
+the GPUs, B ~ N(0, 1/sqrt(K)) column-major replicated, fp32 accumulate, bf16 C
+reassembled on every GPU with an NCCL all-gather.  One step = one pass over the
+whole problem.  `value` is whole-job TFLOP/s (2*M*N*K / step time) with inputs
+resident in HBM; `e2e` is the same metric through the C ABI with HOST buffers
+(host->device copies of A, B, C and the device->host copy of C inside the timed
+region).  Under torchrun (N > 1) every rank runs this file; rank 0 prints the line.
+
+`--impl reference` times the CPU oracle (the restatement of the reference's
+HOST-target loop nest, all host threads) on a bounded slice of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M, N, K = 65536, 8192, 8192
+FLOPS = 2.0 * M * N * K
+METRIC = "gemm_bf16_relu_tflops"
+UNIT = "TFLOP/s"
+WORKLOAD = "sharded bf16 GEMM+ReLU M=65536 N=8192 K=8192 (A row-major by M-row blocks, B col-major replicated, bf16 C all-gathered)"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def mark(self):
+        return time.time()
+
+    def stop(self, t0=None, t1=None):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        for ts, line in self.lines:
+            if t0 is not None and not (t0 - 0.05 <= ts <= t1 + 0.15):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); smax.append(float(parts[2])); power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"], "samples": 0}
+        busy = [c for c, p in zip(sm, power) if p > 250.0] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power)}
+
+
+# ---------------------------------------------------------------------------
+# the reference arm / CPU baseline: the oracle on the host cores
+# ---------------------------------------------------------------------------
+
+def cpu_gemm_sample(rows: int, threads: int, seed: int = 1005):
+    """Times the oracle (fast-math build, `threads` threads) on `rows` rows of the workload; returns seconds."""
+    import numpy as np
+    import oracle
+    rng = np.random.default_rng(seed)
+    a = rng.standard_normal((rows, K), dtype=np.float32)
+    bt = rng.standard_normal((N, K), dtype=np.float32)
+    bt *= np.float32(1.0 / np.sqrt(K))
+    a16 = oracle.f32_to_bf16_bits(a)
+    b16 = oracle.f32_to_bf16_bits(bt).T                 # [K, N] column-major view
+    c16 = np.zeros((rows, N), dtype=np.uint16)
+    af, bf = oracle.bf16_bits_to_f32(a16), oracle.bf16_bits_to_f32(b16)   # widening is not part of the timed GEMM
+    t0 = time.perf_counter()
+    oracle.gemm(af, bf, c16, out_kind="bfloat16", beta=1.0, relu=True, fast=True, threads=threads)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank: int, world: int):
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    threads = oracle.max_threads()
+    rows = 64
+    t = cpu_gemm_sample(rows, threads)                   # calibration, untimed
+    target = 3.0                                         # seconds per step
+    rows = int(max(16, min(8192, rows * target / max(t, 1e-3))))
+    rows -= rows % 16
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_gemm_sample(rows, threads)
+    times = [cpu_gemm_sample(rows, threads) for _ in range(args.steps)]
+    per_step = statistics.mean(times)
+    tflops = 2.0 * rows * N * K / per_step / 1e12
+    sample = f"{rows} of {M} rows per step (same N, K), oracle -O3 -ffast-math, {threads} threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per_step * 1e3 * (M / rows), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+
+def make_inputs(plan, rank, device):
+    """Seeded inputs generated on the host with numpy (the bytes the oracle would see), then moved to HBM."""
+    import numpy as np
+    import torch
+    rng = np.random.default_rng(1005)
+    bt = rng.standard_normal((N, K), dtype=np.float32)
+    bt *= np.float32(1.0 / np.sqrt(K))
+    b_dev = torch.from_numpy(bt).to(device).to(torch.bfloat16).t()          # [K, N] column-major view
+    del bt
+    # A: each rank generates only its own rows, block by block, from per-block seeds
+    parts = []
+    for j in range(plan.chunks):
+        blk = plan.block_of(rank, j)
+        r = np.random.default_rng(2000 + blk)
+        rows_left = plan.block_rows
+        while rows_left > 0:
+            step = min(rows_left, 4096)
+            parts.append(torch.from_numpy(r.standard_normal((step, K), dtype=np.float32)).to(device).to(torch.bfloat16))
+            rows_left -= step
+    a_dev = torch.cat(parts, dim=0)
+    del parts
+    return a_dev, b_dev
+
+
+def timed_steps(fn, steps, warmup, device, dist_on):
+    import torch
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize(device)
+    if dist_on:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    from accera_b200 import runtime as _rt
+    wall0 = time.time()
+    n0 = _rt.launch_count()
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    launches = _rt.launch_count() - n0
+    torch.cuda.synchronize(device)
+    if dist_on:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    wall1 = time.time()
+    ms = start.elapsed_time(end)
+    if dist_on:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps, wall0, wall1, launches
+
+
+def extras_single_gpu(device, peaks):
+    """Device-timed numbers of the other configurations (N=1 only): not the headline, reported beside it."""
+    import torch
+    from accera_b200 import runtime as rt
+    out = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def timeit(fn, iters=20, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize(device)
+        ts = []
+        for _ in range(iters):
+            flush.zero_()                                   # L2 flush: 256 MiB write between timed launches
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(); fn(); e.record()
+            torch.cuda.synchronize(device)
+            ts.append(s.elapsed_time(e) * 1e-3)
+        rt.synchronize()
+        return statistics.median(ts)
+
+    x = torch.randn(1, 8192, 4096, device=device)
+    y = torch.empty(8192, device=device)
+    t = timeit(lambda: rt.reduce_mean_rank3(x, y, [2]))
+    b = 8192 * 4096 * 4 + 8192 * 4
+    out["reduce_mean_f32_8192x4096"] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
+    del x, y
+    T = torch.randn(32000, 4096, device=device) * 0.02
+    idx = torch.randint(0, 32000, (16384, 1), device=device)
+    o = torch.empty(16384, 1, 4096, device=device)
+    t = timeit(lambda: rt.gather_rank2(T, idx, o, 0))
+    b = 2 * 16384 * 4096 * 4 + 16384 * 8
+    out["gather_f32_32000x4096_idx16384"] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
+    del T, idx, o
+    A = torch.rand(512, 512, device=device); B = torch.rand(512, 512, device=device); C = torch.zeros(512, 512, device=device)
+    t = timeit(lambda: rt.gemm(A, B, C, relu=True, compute="simt"))
+    out["matmul_relu_f32_simt_512"] = {"us": t * 1e6, "TFLOP/s": 2 * 512 ** 3 / t / 1e12}
+    A = (torch.rand(4096, 4096, device=device) * 2 - 1).half(); B = (torch.rand(4096, 4096, device=device) * 2 - 1).half().t()
+    C = torch.zeros(4096, 4096, device=device)
+    t = timeit(lambda: rt.gemm(A, B, C, relu=True, compute="tensor_2sm"), iters=10)
+    out["gemm_f16_f32acc_relu_4096"] = {"us": t * 1e6, "TFLOP/s": 2 * 4096 ** 3 / t / 1e12,
+                                        "frac_bf16_peak": 2 * 4096 ** 3 / t / 1e12 / peaks["bf16_tflops"]}
+    A = torch.randint(-128, 128, (8192, 8192), device=device, dtype=torch.int8)
+    B = torch.randint(-128, 128, (8192, 8192), device=device, dtype=torch.int8).t()
+    C = torch.zeros(8192, 8192, device=device, dtype=torch.int32)
+    t = timeit(lambda: rt.gemm(A, B, C, compute="tensor_2sm"), iters=10)
+    out["gemm_s8_s32_8192"] = {"us": t * 1e6, "TOP/s": 2 * 8192 ** 3 / t / 1e12,
+                               "frac_nominal_int8_peak(2x measured bf16)": 2 * 8192 ** 3 / t / 1e12 / (2 * peaks["bf16_tflops"])}
+    return out
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from accera_b200 import runtime as rt
+    from accera_b200.sharded import RowBlockPlan, ShardedGemm
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback (use --impl reference for the CPU arm)")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    dist_on = world > 1
+    if dist_on:
+        dist.init_process_group("nccl", device_id=device)
+    peaks = load_peaks()
+    plan = RowBlockPlan.choose(M, world, max_chunks=args.chunks)
+    a_dev, b_dev = make_inputs(plan, rank, device)
+    c_full = torch.zeros(M, N, dtype=torch.bfloat16, device=device)
+    compute = args.compute
+
+    def gemm_fn(a, b, c):
+        # beta = 1: the HAT function is "C += A @ B, then ReLU" with C INPUT_OUTPUT; the step zeroes its C blocks first
+        rt.gemm(a, b, c, beta=1.0, relu=True, compute=compute)
+
+    sg = ShardedGemm(plan, rank, gemm_fn=gemm_fn)
+    own_blocks = [plan.global_row_range(rank, j) for j in range(plan.chunks)]
+
+    def step():
+        for g0, g1 in own_blocks:
+            c_full[g0:g1].zero_()
+        sg.run(a_dev, b_dev, c_full)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_per_step, wall0, wall1, gpu_launches = timed_steps(step, args.steps, args.warmup, device, dist_on)
+    rt.synchronize()
+    clocks = sampler.stop(wall0, wall1) if rank == 0 else None
+    value = FLOPS / (ms_per_step * 1e-3) / 1e12
+
+    # kernel-only time of the dominant kernel (this rank's GEMM launches), CUDA events on the launching stream
+    def gemm_only():
+        for j in range(plan.chunks):
+            l0, l1 = plan.local_row_range(j)
+            g0, g1 = plan.global_row_range(rank, j)
+            gemm_fn(a_dev[l0:l1], b_dev, c_full[g0:g1])
+    kernel_ms, _, _, _ = timed_steps(gemm_only, args.steps, 1, device, dist_on)
+    kernel_tflops = (FLOPS / world) / (kernel_ms * 1e-3) / 1e12
+
+    # end to end through the C ABI with host buffers (pinned): H2D of A, B, C; GEMM; D2H of C
+    rows_local = plan.rows_per_rank
+    a_host = torch.empty(rows_local, K, dtype=torch.bfloat16).pin_memory()
+    a_host.copy_(a_dev)
+    b_host = torch.empty(N, K, dtype=torch.bfloat16).pin_memory()
+    b_host.copy_(b_dev.t())
+    c_host = torch.zeros(rows_local, N, dtype=torch.bfloat16).pin_memory()
+    a_np = a_host.view(torch.int16).numpy().view(np.uint16)
+    b_np = b_host.view(torch.int16).numpy().view(np.uint16).T          # [K, N] column-major view
+    c_np = c_host.view(torch.int16).numpy().view(np.uint16)
+    del c_full
+    torch.cuda.empty_cache()
+
+    def e2e_step():
+        c_np.fill(0)
+        rt.set_device(local_rank)
+        rt.set_stream(0)
+        rt.gemm(a_np, b_np, c_np, beta=1.0, relu=True, compute=compute, kind="bfloat16", out_kind="bfloat16")
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    if dist_on:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize(device)
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if dist_on:
+        t = torch.tensor([e2e_s], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = FLOPS / e2e_s / 1e12
+    h2d = world * (rows_local * K * 2 + N * K * 2 + rows_local * N * 2)
+    d2h = world * rows_local * N * 2
+    rt.release_workspace()
+
+    extras = None
+    cpu_baseline = None
+    if rank == 0 and world == 1:
+        if not args.no_extras:
+            del a_dev
+            torch.cuda.empty_cache()
+            extras = extras_single_gpu(device, peaks)
+        try:
+            import oracle
+            oracle.build()
+            threads = oracle.max_threads()
+            rows = 64
+            t = cpu_gemm_sample(rows, threads)
+            rows = int(max(16, min(4096, rows * 10.0 / max(t, 1e-3))))
+            rows -= rows % 16
+            t = cpu_gemm_sample(rows, threads)
+            cpu_baseline = {"value": 2.0 * rows * N * K / t / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
+                            "sample": f"{rows} of {M} rows (same N, K), oracle -O3 -ffast-math, {threads} threads, {t:.1f} s"}
+        except Exception as exc:       # the baseline is reported, never required for the GPU numbers
+            cpu_baseline = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {exc!r}"}
+
+    if rank == 0:
+        peak = peaks["bf16_tflops"]
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "compute": compute,
+                       "row_blocks": f"{plan.world * plan.chunks} blocks of {plan.block_rows} rows, block-cyclic",
+                       "chunks": plan.chunks, "l2": "inputs larger than L2 (A shard >= 128 MiB, B 128 MiB, C 1 GiB)",
+                       "beta": 1.0, "peaks": peaks["source"]},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+            "gpu_launches": gpu_launches,
+            "roofline": {"bound": "tensor", "achieved": kernel_tflops,
+                         "peak": peak, "unit": "TFLOP/s", "frac": kernel_tflops / peak,
+                         "frac_of_sustained_peak": (kernel_tflops / peaks["bf16_tflops_sustained"]) if peaks.get("bf16_tflops_sustained") else None,
+                         "traffic": None, "kernel": "gemm_umma_kernel<bf16,cta_group::2>" if compute == "tensor_2sm" else "gemm_umma_kernel<bf16>",
+                         "per": "GPU", "peak_source": peaks["source"] + " burst bf16 (cuBLAS)"},
+            "cpu_baseline": cpu_baseline,
+        }
+        if extras is not None:
+            line["other_configs"] = extras
+        print(json.dumps(line), flush=True)
+    if dist_on:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--compute", default="tensor_2sm", choices=["tensor", "tensor_2sm"])
+    ap.add_argument("--chunks", type=int, default=2, help="row-block rounds per rank for GEMM / all-gather overlap (N > 1)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the device-timed numbers of the other configurations")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world == 1 and args.gpus > 1 and args.impl == "ours":
+        # convenience: `python bench.py --gpus N` re-launches itself under torchrun, one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29541"), __file__] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3                                   # timing rule: at least 3 warm-up steps
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    args.gpus = world
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

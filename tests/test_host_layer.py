@@ -1,0 +1,381 @@
+"""CPU-only tests of the host side: DSL capture, operator recognition, package build (.hat + stub library),
+HAT round trip, loader argument checks, C-ABI exports.  No compute call is made (there is no GPU here and
+no CPU fallback in the product)."""
+import ctypes
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+import accera_b200 as acc
+from accera_b200 import hat, patterns, runtime
+from accera_b200.hat import hat_file
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def quickstart_package():
+    """The reference's README quickstart (README.md:53-91), verbatim apart from the import name."""
+    A = acc.Array(role=acc.Role.INPUT, shape=(512, 512))
+    B = acc.Array(role=acc.Role.INPUT, shape=(512, 512))
+    C = acc.Array(role=acc.Role.INPUT_OUTPUT, shape=(512, 512))
+    matmul = acc.Nest(shape=(512, 512, 512))
+    i1, j1, k1 = matmul.get_indices()
+
+    @matmul.iteration_logic
+    def _():
+        C[i1, j1] += A[i1, k1] * B[k1, j1]
+
+    relu = acc.Nest(shape=(512, 512))
+    i2, j2 = relu.get_indices()
+
+    @relu.iteration_logic
+    def _():
+        C[i2, j2] = acc.max(C[i2, j2], 0.0)
+
+    package = acc.Package()
+    schedule = acc.fuse(matmul.create_schedule(), relu.create_schedule(), partial=2)
+    package.add(schedule, args=(A, B, C), base_name="matmul_relu_fusion_naive")
+    i, j, f, k = schedule.get_indices()
+    ii, jj = schedule.tile({i: 16, j: 16})
+    schedule.reorder(j, i, f, k, jj, ii)
+    plan = schedule.create_plan()
+    plan.unroll(ii)
+    package.add(plan, args=(A, B, C), base_name="matmul_relu_fusion_transformed")
+    return package
+
+
+def test_c_abi_library_exports_every_declared_symbol():
+    lib = runtime.lib()
+    header = open(os.path.join(ROOT, "include", "accera_b200.h")).read()
+    declared = set(re.findall(r"\b(accb_\w+)\s*\(", header))
+    assert declared == set(runtime.EXPORTED_SYMBOLS)
+    out = subprocess.run(["nm", "-D", "--defined-only", runtime.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    exported = set(re.findall(r"\bT (accb_\w+)", out))
+    assert declared <= exported
+    for sym in declared:
+        getattr(lib, sym)
+    assert b"sm_100a" in lib.accb_version()
+
+
+def test_no_cpu_fallback_compute_fails_loudly_without_gpu():
+    if runtime.device_count() > 0:
+        pytest.skip("a GPU is visible")
+    a = np.zeros((4, 4), np.float32)
+    with pytest.raises(runtime.AccbError) as ei:
+        runtime.gemm(a, a, a.copy())
+    assert ei.value.code == runtime.ERR_CUDA
+    with pytest.raises(runtime.AccbError):
+        runtime.reduce_mean_rank3(np.zeros((1, 2, 3), np.float32), np.zeros(2, np.float32), [2])
+    with pytest.raises(runtime.AccbError):
+        runtime.gather_rank2(a, np.zeros((1, 1), np.int64), np.zeros((1, 1, 4), np.float32), 0)
+
+
+def test_host_only_dim_helpers():
+    assert runtime.gather_rank2_dims(5, 4, 2, 3, 0) == (2, 3, 4)
+    assert runtime.gather_rank2_dims(5, 4, 2, 3, 1) == (5, 2, 3)
+    assert runtime.reduce_mean_rank3_dims(2, 3, 4, [2], 0)[0] == (2, 3)
+    assert runtime.reduce_mean_rank3_dims(2, 3, 4, [0, 2], 1)[0] == (1, 3, 1)
+    assert runtime.reduce_mean_rank3_dims(2, 3, 4, [], 0)[0] == (1,)
+
+
+def test_argument_validation_happens_before_any_cuda_call():
+    lib = runtime.lib()
+    d = runtime.GemmDesc()
+    d.m, d.n, d.k = 4, 4, -1
+    assert lib.accb_gemm(ctypes.byref(d), None, None, None, None) == runtime.ERR_ARG
+    assert b"negative" in lib.accb_last_error()
+    assert lib.accb_gemm(None, None, None, None, None) == runtime.ERR_ARG
+    assert lib.accb_gather_rank2(None, 1, 1, None, 1, 1, None, 2, 4) == runtime.ERR_ARG
+    assert lib.accb_gather_rank2(None, 1, 1, None, 1, 1, None, 0, 3) == runtime.ERR_ARG
+    assert lib.accb_reduce_mean_rank3(None, 1, 1, 1, None, 9) == runtime.ERR_ARG
+
+
+def test_quickstart_builds_hat_dynamic_package(tmp_path):
+    package = quickstart_package()
+    files = package.build(name="hello_accera", format=acc.Package.Format.HAT_DYNAMIC, output_dir=str(tmp_path))
+    assert [os.path.basename(f) for f in files] == ["hello_accera.hat", "hello_accera.so"]
+    hf = hat.HATFile.Deserialize(files[0])
+    assert hf.name == "hello_accera"
+    names = [f.name for f in hf.functions]
+    assert len(names) == 2 and re.fullmatch(r"matmul_relu_fusion_naive_[0-9a-f]{16}", names[0])
+    f0 = hf.functions[0]
+    assert f0.calling_convention == "cdecl"
+    assert [a.usage for a in f0.arguments] == ["input", "input", "input_output"]
+    assert all(a.logical_type == "affine_array" and a.declared_type == "float*" and a.shape == [512, 512]
+               and a.affine_map == [512, 1] and a.affine_offset == 0 for a in f0.arguments)
+    assert f0.return_info.logical_type == "void"
+    assert f0.auxiliary["accera"]["parameters"] == {}
+    assert f0.auxiliary["accera_b200"]["relu"] is True and f0.auxiliary["accera_b200"]["compute"] == "simt"
+    assert hf.dependencies["link_target"] == "hello_accera.so"
+    assert hf.target["required"]["GPU"]["instruction_set_version"] == "sm_100a"
+    # header text: unnamed-parameter prototypes and guarded aliases (TranslateToHeader.cpp:402-506)
+    assert f"void {names[0]}(float*, float*, float*);" in hf.declaration_code
+    assert f"void (*matmul_relu_fusion_naive)(float*, float*, float*) = {names[0]};" in hf.declaration_code
+    assert "#ifndef __matmul_relu_fusion_naive_DEFINED__" in hf.declaration_code
+    # the library exports exactly those symbols
+    out = subprocess.run(["nm", "-D", "--defined-only", files[1]], capture_output=True, text=True, check=True).stdout
+    for n in names:
+        assert re.search(rf"\bT {n}\b", out)
+    # and the same file is a usable C header
+    src = tmp_path / "client.c"
+    src.write_text('#include "hello_accera.hat"\nint main(void) { return matmul_relu_fusion_naive == 0; }\n')
+    subprocess.run(["gcc", "-c", str(src), "-I", str(tmp_path), "-o", str(tmp_path / "client.o")], check=True)
+
+
+def test_function_names_are_stable_and_depend_on_signature():
+    p1, p2 = quickstart_package(), quickstart_package()
+    assert list(p1._fns) == list(p2._fns)
+    A = acc.Array(role=acc.Role.INPUT, shape=(256, 512))
+    B = acc.Array(role=acc.Role.INPUT, shape=(512, 512))
+    C = acc.Array(role=acc.Role.INPUT_OUTPUT, shape=(256, 512))
+    n = acc.Nest(shape=(256, 512, 512))
+    i, j, k = n.get_indices()
+
+    @n.iteration_logic
+    def _():
+        C[i, j] += A[i, k] * B[k, j]
+    p3 = acc.Package()
+    fn = p3.add(n, args=(A, B, C), base_name="matmul_relu_fusion_naive")
+    assert fn.name not in p1._fns and fn.name.startswith("matmul_relu_fusion_naive_")
+    assert p3.add(n, args=(A, B, C)).name.startswith("_")          # no base name: anonymous hashed name
+
+
+def _gemm_nest(m, n, k, et_in, et_out, b_layout=acc.Layout.FIRST_MAJOR, transposed_b=False):
+    A = acc.Array(role=acc.Role.INPUT, element_type=et_in, shape=(m, k))
+    B = acc.Array(role=acc.Role.INPUT, element_type=et_in, shape=(n, k) if transposed_b else (k, n), layout=b_layout)
+    C = acc.Array(role=acc.Role.INPUT_OUTPUT, element_type=et_out, shape=(m, n))
+    nest = acc.Nest(shape=(m, n, k))
+    i, j, kk = nest.get_indices()
+
+    @nest.iteration_logic
+    def _():
+        if transposed_b:
+            C[i, j] += acc.cast(A[i, kk], et_out) * acc.cast(B[j, kk], et_out)
+        else:
+            C[i, j] += A[i, kk] * B[kk, j]
+    return nest, (A, B, C)
+
+
+def test_recognise_tensorized_gemm_with_fragment_ops():
+    nest, (A, B, C) = _gemm_nest(4096, 4096, 4096, acc.ScalarType.float16, acc.ScalarType.float32, acc.Layout.LAST_MAJOR)
+    target = acc.Target(acc.Target.Model.NVIDIA_B200)
+    plan = nest.create_schedule().create_plan(target)
+    i, j, k = nest.get_indices()
+    plan.tensorize(indices=(i, j, k), mma_shape=acc.MMAShape.M16xN16xK16_B1, prologue_op=acc.MMAFragmentOp.SET,
+                   prologue_arg=0, epilogue_op=acc.MMAFragmentOp.ReLU)
+    spec = patterns.recognise(plan)
+    assert spec.kind == "gemm" and spec.compute == "tensor" and spec.relu and spec.beta == 0.0 and spec.alpha == 1.0
+    assert B.strides() == (1, 4096) and A.strides() == (4096, 1)
+    plan2 = nest.create_schedule().create_plan(target)
+    plan2.tensorize(indices=(i, j, k), mma_shape=acc.MMAShape.M16xN16xK16_B1, prologue_op=acc.MMAFragmentOp.SCALE,
+                    prologue_arg=0.5, epilogue_op=acc.MMAFragmentOp.SCALE, epilogue_arg=4.0)
+    spec2 = patterns.recognise(plan2)
+    assert spec2.alpha == 4.0 and spec2.beta == 2.0 and not spec2.relu      # 4 * (0.5 * C + A @ B)
+
+
+def test_recognise_transposed_operand_with_casts():
+    # int_matmul_tests.py:55 form: C[i,j] += cast(A[i,k]) * cast(B[j,k])
+    nest, _ = _gemm_nest(64, 32, 128, acc.ScalarType.int8, acc.ScalarType.int32, transposed_b=True)
+    spec = patterns.recognise(nest)
+    assert spec.kind == "gemm" and spec.b_transposed and not spec.a_transposed and (spec.m, spec.n, spec.k) == (64, 32, 128)
+
+
+def test_bias_relu_fusion_and_rejections():
+    m, n, k = 64, 48, 32
+    A = acc.Array(role=acc.Role.INPUT, shape=(m, k)); B = acc.Array(role=acc.Role.INPUT, shape=(k, n))
+    C = acc.Array(role=acc.Role.INPUT_OUTPUT, shape=(m, n)); bias = acc.Array(role=acc.Role.INPUT, shape=(n,))
+    mm = acc.Nest((m, n, k)); i, j, kk = mm.get_indices()
+
+    @mm.iteration_logic
+    def _():
+        C[i, j] += A[i, kk] * B[kk, j]
+    bn = acc.Nest((m, n)); bi, bj = bn.get_indices()
+
+    @bn.iteration_logic
+    def _():
+        C[bi, bj] += bias[bj]
+    rn = acc.Nest((m, n)); ri, rj = rn.get_indices()
+
+    @rn.iteration_logic
+    def _():
+        C[ri, rj] = acc.max(0.0, C[ri, rj])
+    spec = patterns.recognise(acc.fuse((mm, bn, rn), partial=2))
+    assert spec.bias is bias and spec.relu
+    with pytest.raises(patterns.UnsupportedNestError):
+        patterns.recognise(acc.fuse((mm, rn, bn), partial=2))          # nothing may follow the ReLU
+    other = acc.Nest((m, n)); oi, oj = other.get_indices()
+
+    @other.iteration_logic
+    def _():
+        C[oi, oj] = C[oi, oj] * 2.0
+    with pytest.raises(patterns.UnsupportedNestError):
+        patterns.recognise(other)                                       # not one of the implemented operators
+    pkg = acc.Package()
+    with pytest.raises(ValueError):
+        pkg.add(acc.fuse((mm, bn, rn), partial=2), args=(A, B, C), base_name="x")   # bias missing from args
+
+
+def test_single_target_rule_and_temp_args():
+    nest, args = _gemm_nest(64, 64, 64, acc.ScalarType.float32, acc.ScalarType.float32)
+    pkg = acc.Package()
+    pkg.add(nest, args=args, base_name="host_fn")
+    gpu_plan = nest.create_schedule().create_plan(acc.Target(acc.Target.Model.NVIDIA_B200))
+    with pytest.raises(NotImplementedError):                             # unit_tests.py:218
+        pkg.add(gpu_plan, args=args, base_name="gpu_fn")
+    T = acc.Array(role=acc.Role.TEMP, shape=(4, 4))
+    with pytest.raises(ValueError):
+        pkg.add(nest, args=(T,) + tuple(args), base_name="bad")
+
+
+def gather_package(axis):
+    """dsl_tests.py:1571-1675: a dimension function and a compute function per axis."""
+    DataDim0, DataDim1, IndicesDim0, IndicesDim1 = acc.create_dimensions()
+    OutputDim0, OutputDim1, OutputDim2 = acc.create_dimensions(acc.Role.OUTPUT)
+    Data = acc.Array(shape=(DataDim0, DataDim1), role=acc.Role.INPUT)
+    Indices = acc.Array(shape=(IndicesDim0, IndicesDim1), role=acc.Role.INPUT, element_type=acc.ScalarType.index)
+    package = acc.Package()
+    if axis == 0:
+        Output = acc.Array(shape=(IndicesDim0, IndicesDim1, DataDim1), role=acc.Role.INPUT_OUTPUT)
+        nest_dims = acc.Nest((1, ))
+
+        @nest_dims.iteration_logic
+        def _():
+            OutputDim0.set(IndicesDim0)
+            OutputDim1.set(IndicesDim1)
+            OutputDim2.set(DataDim1)
+        nest_array = acc.Nest((IndicesDim0, IndicesDim1, DataDim1))
+        i, j, k = nest_array.get_indices()
+
+        @nest_array.iteration_logic
+        def _():
+            Output[i, j, k] = Data[Indices[i, j], k]
+        package.add(nest_dims, args=(DataDim1, IndicesDim0, IndicesDim1, OutputDim0, OutputDim1, OutputDim2),
+                    base_name=f"Gather_rank_2_dim_axis_{axis}")
+        package.add(nest_array, args=(IndicesDim0, IndicesDim1, DataDim0, DataDim1, Output, Data, Indices),
+                    base_name=f"Gather_rank_2_array_axis_{axis}")
+    else:
+        Output = acc.Array(shape=(DataDim0, IndicesDim0, IndicesDim1), role=acc.Role.INPUT_OUTPUT)
+        nest_dims = acc.Nest((1, ))
+
+        @nest_dims.iteration_logic
+        def _():
+            OutputDim0.set(DataDim0)
+            OutputDim1.set(IndicesDim0)
+            OutputDim2.set(IndicesDim1)
+        nest_array = acc.Nest((DataDim0, IndicesDim0, IndicesDim1))
+        i, j, k = nest_array.get_indices()
+
+        @nest_array.iteration_logic
+        def _():
+            Output[i, j, k] = Data[i, Indices[j, k]]
+        package.add(nest_dims, args=(DataDim0, IndicesDim0, IndicesDim1, OutputDim0, OutputDim1, OutputDim2),
+                    base_name=f"Gather_rank_2_dim_axis_{axis}")
+        package.add(nest_array, args=(DataDim0, IndicesDim0, IndicesDim1, DataDim1, Output, Data, Indices),
+                    base_name=f"Gather_rank_2_array_axis_{axis}")
+    return package
+
+
+@pytest.mark.parametrize("axis", [0, 1])
+def test_gather_package_prototypes_and_dimension_function(tmp_path, axis):
+    package = gather_package(axis)
+    files = package.build("test_output_array_gather_node", format=acc.Package.Format.HAT_DYNAMIC, output_dir=str(tmp_path))
+    hf = hat.HATFile.read(files[0])
+    dim_fn, arr_fn = hf.functions
+    assert dim_fn.c_declaration().endswith("(int64_t, int64_t, int64_t, int64_t*, int64_t*, int64_t*);")
+    assert arr_fn.c_declaration().endswith("(int64_t, int64_t, int64_t, int64_t, float*, float*, int64_t*);")
+    out_arg = arr_fn.arguments[4]
+    assert out_arg.logical_type == "runtime_array" and out_arg.usage == "input_output"
+    assert out_arg.size == ("IndicesDim0*IndicesDim1*DataDim1" if axis == 0 else "DataDim0*IndicesDim0*IndicesDim1")
+    assert arr_fn.arguments[6].element_type == "int64_t"
+    # the dimension function is pure host code: call it through the loader
+    _, fns = hat.load(files[0])
+    o = [np.zeros(1, np.int64) for _ in range(3)]
+    fns[f"Gather_rank_2_dim_axis_{axis}"](7, 2, 3, *o)
+    assert [int(x[0]) for x in o] == [2, 3, 7] if axis == 0 else [7, 2, 3]
+
+
+def test_reduce_mean_recognition_static_and_package(tmp_path):
+    data = acc.Array(role=acc.Role.INPUT, shape=(8192, 4096))
+    red = acc.Array(role=acc.Role.INPUT_OUTPUT, shape=(8192,))
+    init = acc.Nest((8192,)); (i0) = init.get_indices()
+
+    @init.iteration_logic
+    def _():
+        red[i0] = acc.cast(0, acc.ScalarType.float32)
+    accn = acc.Nest((8192, 4096)); r, c = accn.get_indices()
+
+    @accn.iteration_logic
+    def _():
+        red[r] += data[r, c]
+    div = acc.Nest((8192,)); i1 = div.get_indices()
+
+    @div.iteration_logic
+    def _():
+        red[i1] /= acc.cast(4096, acc.ScalarType.float32)
+    sched = acc.fuse((init, accn, div), partial=1)
+    spec = patterns.recognise(sched)
+    assert spec.kind == "reduce_mean" and spec.axes == (1,) and spec.keepdims == 0
+    pkg = acc.Package()
+    pkg.add(sched, args=(data, red), base_name="ReduceMean_rows")
+    files = pkg.build("reduce_pkg", format=acc.Package.Format.HAT_DYNAMIC | acc.Package.Format.SOURCE, output_dir=str(tmp_path))
+    src = open([f for f in files if f.endswith(".cpp")][0]).read()
+    assert "accb_reduce_mean_rank3(a0, INT64_C(1), INT64_C(8192), INT64_C(4096), a1, 4)" in src
+
+
+def test_hat_round_trip_preserves_description_and_functions(tmp_path):
+    pkg = quickstart_package()
+    pkg.add_description(author="someone", license="https://example.org/license", version="1.2",
+                        other={"title": "quickstart", "nested": {"a": 1}})        # dsl_tests.py:6398-6449
+    files = pkg.build("meta_pkg", output_dir=str(tmp_path))
+    hf = hat.HATFile.Deserialize(files[0])
+    assert hf.description["author"] == "someone" and hf.description["version"] == "1.2"
+    assert hf.description["license_url"] == "https://example.org/license"
+    assert hf.description["auxiliary"] == {"title": "quickstart", "nested": {"a": 1}}
+    out = tmp_path / "copy.hat"
+    hf.Serialize(str(out))
+    again = hat.HATFile.Deserialize(str(out))
+    assert [f.name for f in again.functions] == [f.name for f in hf.functions]
+    assert again.functions[0].arguments == hf.functions[0].arguments
+    assert again.declaration_code.strip() == hf.declaration_code.strip()
+    assert again.dependencies == hf.dependencies and again.target == hf.target
+
+
+def test_loader_checks_arguments_against_descriptor(tmp_path):
+    nest, args = _gemm_nest(64, 32, 48, acc.ScalarType.float16, acc.ScalarType.float32, acc.Layout.LAST_MAJOR)
+    pkg = acc.Package()
+    pkg.add(nest, args=args, base_name="mm")
+    files = pkg.build("chk", output_dir=str(tmp_path))
+    package, fns = hat.load(files[0])
+    assert len(fns.names) == 1 and "mm" in fns and fns.mm is fns[fns.names[0]]
+    assert package.get_functions()[0].auxiliary["accera"]["parameters"] == {}      # dsl_tests.py:5787-5842
+    A = np.zeros((64, 48), np.float16); B = np.zeros((48, 32), np.float16); C = np.zeros((64, 32), np.float32)
+    with pytest.raises(ValueError, match="order='F'"):
+        fns.mm(A, B, C)                                    # B is LAST_MAJOR in the descriptor
+    with pytest.raises(TypeError):
+        fns.mm(A.astype(np.float32), np.asfortranarray(B), C)
+    with pytest.raises(ValueError):
+        fns.mm(A[:32], np.asfortranarray(B), C)
+    with pytest.raises(ValueError):
+        fns.mm(A, np.asfortranarray(B))
+
+
+def test_static_package_and_format_rules(tmp_path):
+    pkg = quickstart_package()
+    files = pkg.build("static_pkg", format=acc.Package.Format.HAT_STATIC, output_dir=str(tmp_path))
+    assert [os.path.basename(f) for f in files] == ["static_pkg.hat", "static_pkg.a"]
+    assert hat.HATFile.read(files[0]).dependencies["link_target"] == "static_pkg.a"
+    with pytest.raises(RuntimeError):
+        hat.load(files[0])
+    with pytest.raises(NotImplementedError):
+        pkg.build("dbg", mode=acc.Package.Mode.DEBUG, output_dir=str(tmp_path))
+
+
+def test_benchmark_statistics_fields():
+    r = hat.BenchmarkResult("f", [3.0, 1.0, 2.0, 10.0, 1.5])
+    d = r.as_dict()
+    assert set(d) == {"function_name", "mean", "median_of_means", "mean_of_small_means", "robust_mean", "min_of_means"}
+    assert d["min_of_means"] == 1.0 and d["median_of_means"] == 2.0 and d["mean"] == pytest.approx(3.5)
+    assert d["robust_mean"] == pytest.approx((1.5 + 2.0 + 3.0) / 3)
