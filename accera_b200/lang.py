@@ -394,7 +394,12 @@ class Array:
         self.element_type = element_type
         self.layout = layout
         self.offset = offset
-        self.shape = tuple(shape)
+        self._shape = tuple(shape)
+
+    @property
+    def shape(self) -> list:
+        """A fresh list, as in the reference (lang/Array.py:152-154): callers concatenate and edit it."""
+        return list(self._shape)
 
     @property
     def is_dynamic(self) -> bool:
@@ -448,8 +453,9 @@ class Nest:
         self.statements: List[Statement] = []
         self._logic_fns: List[Callable] = []
 
-    def get_indices(self):
-        return self._indices[0] if len(self._indices) == 1 else list(self._indices)
+    def get_indices(self) -> List[Index]:
+        """Always a list, also for a rank-1 nest (lang/Nest.py:62-86)."""
+        return list(self._indices)
 
     def iteration_logic(self, fn: Callable) -> Callable:
         _trace_stack.append([])
@@ -475,22 +481,24 @@ class Schedule:
     the other, each running all of its remaining dimensions - the "fusing index precedes the
     unfused ones" rule of docs/Reference/safety_analysis.md:28-34.
     """
-    def __init__(self, nests: List[Nest], partial: Optional[int] = None):
+    def __init__(self, nests: List[Nest], partial: Optional[int] = None, orders: Optional[List[List[Index]]] = None):
         self.nests = list(nests)
         self.partial = partial
         self.transformations: List[Tuple[str, Any]] = []
+        # per nest: its own indices in the loop order they had when the schedule was built / fused
+        self.orders: List[List[Index]] = [list(o) for o in orders] if orders else [list(n._indices) for n in nests]
         if len(nests) == 1:
-            self._indices = list(nests[0]._indices)
+            self._indices = list(self.orders[0])
         else:
-            fused = [Index(nests[0].shape[d], None, d, f"f{d}") for d in range(partial)]
+            fused = [Index(self.orders[0][d].extent, None, d, f"f{d}") for d in range(partial)]
             fusing = Index(len(nests), None, partial, "f")
             rest: List[Index] = []
-            for n in nests:
-                rest.extend(n._indices[partial:])
+            for o in self.orders:
+                rest.extend(o[partial:])
             self._indices = fused + [fusing] + rest
 
-    def get_indices(self):
-        return self._indices[0] if len(self._indices) == 1 else list(self._indices)
+    def get_indices(self) -> List[Index]:
+        return list(self._indices)
 
     def get_fusing_index(self) -> Index:
         return self._indices[self.partial] if self.partial is not None else None
@@ -517,6 +525,9 @@ class Schedule:
             raise ValueError("reorder must name every index of the schedule exactly once")
         self.transformations.append(("reorder", order))
         self._indices = list(order)
+        if len(self.nests) == 1:
+            own = set(map(id, self.nests[0]._indices))
+            self.orders[0] = [ix for ix in order if id(ix) in own]
 
     def skew(self, index, reference_index, unroll_loops_smaller_than=None):
         self.transformations.append(("skew", (index, reference_index)))
@@ -532,20 +543,23 @@ def fuse(*args, partial: Optional[int] = None) -> Schedule:
     """fuse(s0, s1, ..., partial=n) or fuse((s0, s1, ...), partial=n)."""
     scheds = list(args[0]) if len(args) == 1 and isinstance(args[0], (tuple, list)) else list(args)
     nests: List[Nest] = []
+    orders: List[List[Index]] = []
     for s in scheds:
         if isinstance(s, Nest):
             s = s.create_schedule()
         if not isinstance(s, Schedule):
             raise TypeError("fuse takes schedules")
         nests.extend(s.nests)
+        orders.extend(s.orders)
     if partial is None:
-        partial = builtins_min(len(n.shape) for n in nests)
-    for n in nests:
-        if len(n.shape) < partial:
+        partial = builtins_min(len(o) for o in orders)
+    first = [ix.extent for ix in orders[0][:partial]]
+    for o in orders:
+        if len(o) < partial:
             raise ValueError("partial exceeds a nest's rank")
-        if tuple(n.shape[:partial]) != tuple(nests[0].shape[:partial]):
+        if [ix.extent for ix in o[:partial]] != first:
             raise ValueError("fused dimensions must have equal extents")
-    return Schedule(nests, partial)
+    return Schedule(nests, partial, orders)
 
 
 import builtins as _builtins  # noqa: E402

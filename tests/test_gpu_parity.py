@@ -418,3 +418,47 @@ def test_gemm_int8_8192_config():
     lhs = got.astype(np.int64) @ v
     rhs = A.astype(np.int64) @ (B.astype(np.int64) @ v)
     assert np.array_equal(lhs, rhs)
+
+
+# ---------------------------------------------------------------------------
+# golden vectors made from the reference's own Python sources (tests/golden/make_golden.py)
+# ---------------------------------------------------------------------------
+
+import os as _os
+
+_GOLDEN = _os.path.join(_os.path.dirname(_os.path.abspath(__file__)), "golden")
+
+
+def test_golden_matmul_relu_quickstart():
+    g = np.load(_os.path.join(_GOLDEN, "matmul_relu.npz"))
+    for name in ("unit", "signed"):
+        A, B, C0, want = g[f"{name}_A"], g[f"{name}_B"], g[f"{name}_C_in"], g[f"{name}_C_out"]
+        got = C0.copy()
+        rt.gemm(A, B, got, relu=True, compute="simt")
+        _assert_close(got, want, _gemm_scale(A, B) + np.abs(C0), RTOL_F32, f"golden matmul_relu {name}")
+        assert np.array_equal(got == 0, want == 0) or name == "signed"
+
+
+def test_golden_reduce_mean_all_axes():
+    g = np.load(_os.path.join(_GOLDEN, "reduce_mean.npz"))
+    data = g["data"]
+    for k in [k for k in g.files if k != "data"]:
+        axes, keep = [int(c) for c in k.split("_")[0][4:]], int(k[-1])
+        want = g[k]
+        dims, _ = rt.reduce_mean_rank3_dims(*data.shape, axes, keep)
+        assert dims == want.shape
+        got = np.full(want.shape, np.nan, np.float32)
+        rt.reduce_mean_rank3(data, got, axes)
+        scale = np.abs(data).astype(np.float64).mean(axis=tuple(axes), keepdims=bool(keep)).reshape(want.shape)
+        _assert_close(got, want, scale, RTOL_F32, f"golden reduce_mean {k}")
+
+
+def test_golden_gather():
+    g = np.load(_os.path.join(_GOLDEN, "gather.npz"))
+    for name in ("verify", "wide", "single"):
+        data, idx = g[f"{name}_data"], g[f"{name}_indices"]
+        for axis in (0, 1):
+            want = g[f"{name}_axis{axis}"]
+            got = np.empty_like(want)
+            rt.gather_rank2(data, idx, got, axis)
+            assert got.tobytes() == want.tobytes(), (name, axis)

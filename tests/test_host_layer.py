@@ -300,7 +300,7 @@ def test_gather_package_prototypes_and_dimension_function(tmp_path, axis):
 def test_reduce_mean_recognition_static_and_package(tmp_path):
     data = acc.Array(role=acc.Role.INPUT, shape=(8192, 4096))
     red = acc.Array(role=acc.Role.INPUT_OUTPUT, shape=(8192,))
-    init = acc.Nest((8192,)); (i0) = init.get_indices()
+    init = acc.Nest((8192,)); i0, = init.get_indices()
 
     @init.iteration_logic
     def _():
@@ -310,7 +310,7 @@ def test_reduce_mean_recognition_static_and_package(tmp_path):
     @accn.iteration_logic
     def _():
         red[r] += data[r, c]
-    div = acc.Nest((8192,)); i1 = div.get_indices()
+    div = acc.Nest((8192,)); i1, = div.get_indices()
 
     @div.iteration_logic
     def _():
