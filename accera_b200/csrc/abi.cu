@@ -167,6 +167,9 @@ int64_t span_elems(int64_t d0, int64_t d1, const int64_t* st)
 }
 
 }  // namespace
+
+int set_error(int code, const char* msg) { return fail(code, msg ? msg : ""); }
+
 }  // namespace accb
 
 using namespace accb;

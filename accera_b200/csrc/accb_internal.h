@@ -52,4 +52,7 @@ int launch_gather(const void* data, int64_t d0, int64_t d1, const int64_t* indic
 // counts kernels launched (reported by accb_launch_count)
 void note_launches(int n);
 
+// records `msg` as the calling thread's last error (what accb_last_error returns) and returns `code`
+int set_error(int code, const char* msg);
+
 }  // namespace accb

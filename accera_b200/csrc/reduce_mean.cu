@@ -17,7 +17,16 @@
 // When there are too few outputs to fill the GPU, each output's reduction is
 // split over several blocks that write fp32 partial sums to a scratch buffer and
 // a second small kernel folds them in a fixed order (deterministic, no atomics).
+#include <mutex>
+#include <string>
+
 #include "accb_internal.h"
+
+// Scratch for accb_reduce_mean_rank3_noalloc: lives in the library image, so every GPU that loads the
+// library carries these 256 KiB until the process exits.  In host code this name is only a handle for
+// cudaGetSymbolAddress; kernels are always given the device address obtained from it.
+constexpr size_t kStaticScratchFloats = 64 * 1024;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 
 namespace accb {
 namespace {
@@ -339,3 +348,81 @@ int launch_reduce_mean(const float* data, int64_t d0, int64_t d1, int64_t d2, fl
 }
 
 }  // namespace accb
+
+// ---------------------------------------------------------------------------------
+// accb_reduce_mean_rank3_noalloc
+// ---------------------------------------------------------------------------------
+
+namespace {
+
+constexpr int kMaxDevicesNoAlloc = 64;
+std::mutex g_noalloc_mu;
+float* g_noalloc_scratch[kMaxDevicesNoAlloc];   // device address of g_static_scratch, per device
+int g_noalloc_sms[kMaxDevicesNoAlloc];
+
+bool on_device(const void* p)
+{
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+}  // namespace
+
+extern "C" int accb_reduce_mean_rank3_noalloc(const float* data, int64_t d0, int64_t d1, int64_t d2, float* reduced,
+                                              int32_t axes_mask, void* cuda_stream)
+{
+    using accb::set_error;
+    if (d0 < 0 || d1 < 0 || d2 < 0) return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: negative dimension");
+    if (axes_mask < 0 || axes_mask > 7) return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: axes_mask must be in [0, 7]");
+    if (axes_mask == 0) axes_mask = 7;
+    const int64_t dims[3] = { d0, d1, d2 };
+    int64_t n_out = 1;
+    for (int d = 0; d < 3; ++d) if (!(axes_mask & (1 << d))) n_out *= dims[d];
+    if (n_out == 0) return ACCB_OK;
+    if (d0 * d1 * d2 == 0) return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: mean over zero elements");
+    if (!data || !reduced) return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: null array pointer");
+
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return set_error(ACCB_ERR_CUDA, cudaGetErrorString(e)); }
+    if (dev < 0 || dev >= kMaxDevicesNoAlloc) return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: device index out of range");
+    if (!on_device(data) || !on_device(reduced))
+        return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: data and reduced must be device memory "
+                                       "(this entry point cannot stage host buffers, it allocates nothing)");
+    float* scratch = nullptr;
+    int sms = 0;
+    {
+        // one-time set-up per device, with that device current: resolve the device address of the array
+        std::lock_guard<std::mutex> lock(g_noalloc_mu);
+        if (g_noalloc_scratch[dev] == nullptr) {
+            float* p = nullptr;
+            e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+            if (e != cudaSuccess || p == nullptr) {
+                (void)cudaGetLastError();
+                return set_error(ACCB_ERR_CUDA, (std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e)).c_str());
+            }
+            int n = 0;
+            e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+            if (e != cudaSuccess || n <= 0) { (void)cudaGetLastError(); return set_error(ACCB_ERR_CUDA, "cudaDeviceGetAttribute(multiProcessorCount) failed"); }
+            g_noalloc_sms[dev] = n;
+            g_noalloc_scratch[dev] = p;
+        }
+        scratch = g_noalloc_scratch[dev];
+        sms = g_noalloc_sms[dev];
+    }
+    const size_t capacity = kStaticScratchFloats * sizeof(float);
+    const size_t need = accb::reduce_mean_scratch_bytes(d0, d1, d2, axes_mask, sms);
+    if (need > capacity) {
+        const std::string msg = "accb_reduce_mean_rank3_noalloc: this shape needs " + std::to_string(need) +
+                                " bytes of partial sums but the built-in scratch holds " + std::to_string(capacity) +
+                                "; use accb_reduce_mean_rank3";
+        return set_error(ACCB_ERR_LIMIT, msg.c_str());
+    }
+    const char* err = "";
+    const int n = accb::launch_reduce_mean(data, d0, d1, d2, reduced, axes_mask, scratch, capacity, sms,
+                                           (cudaStream_t)cuda_stream, &err);
+    if (n < 0) return set_error(n, (std::string("accb_reduce_mean_rank3_noalloc: ") + err).c_str());
+    return ACCB_OK;
+}
+

@@ -30,7 +30,7 @@ _NP_TYPE = {"float32": F32, "float16": F16, "int8": S8, "int32": S32, "uint8": U
 _COMPUTE = {"auto": COMPUTE_AUTO, "simt": COMPUTE_SIMT, "tensor": COMPUTE_TENSOR, "tensor_2sm": COMPUTE_TENSOR_2SM}
 
 EXPORTED_SYMBOLS = (
-    "accb_gemm", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
+    "accb_gemm", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_noalloc", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
     "accb_gather_rank2_dims", "accb_set_device", "accb_set_stream", "accb_synchronize", "accb_last_error",
     "accb_launch_count", "accb_release_workspace", "accb_device_count", "accb_version",
 )
@@ -74,6 +74,8 @@ def lib() -> ctypes.CDLL:
     L.accb_gemm.restype = ctypes.c_int
     L.accb_reduce_mean_rank3.argtypes = [vp, i64, i64, i64, vp, i32]
     L.accb_reduce_mean_rank3.restype = ctypes.c_int
+    L.accb_reduce_mean_rank3_noalloc.argtypes = [vp, i64, i64, i64, vp, i32, vp]
+    L.accb_reduce_mean_rank3_noalloc.restype = ctypes.c_int
     L.accb_reduce_mean_rank3_dims.argtypes = [i64, i64, i64, i32, i32, ctypes.POINTER(i64)]
     L.accb_reduce_mean_rank3_dims.restype = ctypes.c_int
     L.accb_gather_rank2.argtypes = [vp, i64, i64, vp, i64, i64, vp, i32, i32]
@@ -243,6 +245,25 @@ def reduce_mean_rank3(data, reduced, axes) -> None:
     mask = sum(1 << a for a in set(axes))
     _sync_torch_stream(data, reduced)
     _check(lib().accb_reduce_mean_rank3(pd, shd[0], shd[1], shd[2], pr, mask))
+
+
+def reduce_mean_rank3_noalloc(data, reduced, axes, stream_handle: Optional[int] = None) -> None:
+    """Like reduce_mean_rank3 for torch CUDA tensors, through the entry point that never allocates device
+    memory (partial sums go to a 256 KiB array built into the library).  For hosts that own all device
+    memory themselves.  Shapes that would need more scratch raise AccbError(ERR_LIMIT); calls that overlap
+    on the GPU race on the shared array.  Enqueued on `stream_handle` (default: torch's current stream)."""
+    pd, td, shd, _, dd = _describe(data)
+    pr, tr, _, _, dr = _describe(reduced)
+    if td != F32 or tr != F32 or len(shd) != 3:
+        raise ValueError("reduce_mean_rank3_noalloc takes a rank-3 fp32 array")
+    axes = list(range(3)) if not axes else [a % 3 for a in axes]
+    mask = sum(1 << a for a in set(axes))
+    if stream_handle is None and _is_torch(data) and data.is_cuda:
+        import torch
+        set_device(data.device.index)
+        stream_handle = torch.cuda.current_stream(data.device).cuda_stream
+    _check(lib().accb_reduce_mean_rank3_noalloc(pd, shd[0], shd[1], shd[2], pr, mask,
+                                                ctypes.c_void_p(int(stream_handle or 0) or None)))
 
 
 def gather_rank2(data, indices, output, axis: int = 0) -> None:

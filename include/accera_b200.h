@@ -98,6 +98,36 @@ int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c,
  */
 int accb_reduce_mean_rank3(const float* data, int64_t d0, int64_t d1, int64_t d2, float* reduced, int32_t axes_mask);
 
+/*
+ * ReduceMean for callers that must not see a device allocation happen inside the call.
+ * (No counterpart in the reference: it has no GPU reduce_mean and no allocation contract.)
+ *
+ * accb_reduce_mean_rank3 may grow a cached scratch buffer with cudaMalloc when a reduction has
+ * too few outputs to fill the GPU and is split over blocks.  That is wrong for a host that owns
+ * all of device memory itself - an inference server or framework that wraps a HAT function as a
+ * custom operator and hands it buffers from its own arena (a hidden cudaMalloc escapes the arena's
+ * accounting, can fail when the arena already holds nearly all of HBM, and synchronises the whole
+ * device in the middle of a serving loop) - and for code that runs after such a host has frozen
+ * allocation.  This variant computes the same result with the same kernels but keeps the partial
+ * sums in a 256 KiB array compiled into the library, and calls no cudaMalloc, cudaFree or any
+ * other allocating routine.
+ *
+ *  - data and reduced must be DEVICE pointers (there is no staging here); the work is enqueued on
+ *    cuda_stream (a cudaStream_t, NULL = default stream) of the current device and not synchronised.
+ *  - A shape whose split reduction needs more than 256 KiB of partial sums is rejected with
+ *    ACCB_ERR_LIMIT (nothing is launched).  On a 148-SM part the planner asks for at most about
+ *    300 KiB, and only for very wide, short column reductions (tens of thousands of outputs, each
+ *    split in two); everything else fits.  Use accb_reduce_mean_rank3 for the rejected shapes.
+ *  - The first call on each device resolves the array's device address (cudaGetSymbolAddress), so
+ *    make that first call during set-up, before any stream capture begins.
+ *  - Every call on a device shares the one array, and it keeps whatever the previous call left:
+ *    each call overwrites every partial sum it later reads, so nothing needs clearing, but two
+ *    calls that overlap on the GPU (different streams, no ordering) race on it - serialise them.
+ *  - Every GPU that loads the library holds the 256 KiB until the process exits.
+ */
+int accb_reduce_mean_rank3_noalloc(const float* data, int64_t d0, int64_t d1, int64_t d2, float* reduced,
+                                   int32_t axes_mask, void* cuda_stream);
+
 /* host-only helper: writes the output dims, returns the output rank (1..3) */
 int accb_reduce_mean_rank3_dims(int64_t d0, int64_t d1, int64_t d2, int32_t axes_mask, int32_t keepdims,
                                 int64_t* out_dims);
