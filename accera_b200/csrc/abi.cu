@@ -51,6 +51,8 @@ struct DeviceState {
     size_t slot_bytes[4] = { 0, 0, 0, 0 };
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
+    cudaStream_t pipe[2] = { nullptr, nullptr };   // staging pipeline of large host-pointer GEMMs
+    cudaEvent_t pipe_ready = nullptr;              // B (and bias) have arrived
 };
 DeviceState g_dev[kMaxDevices];
 
@@ -170,6 +172,81 @@ int64_t span_elems(int64_t d0, int64_t d1, const int64_t* st)
 
 int set_error(int code, const char* msg) { return fail(code, msg ? msg : ""); }
 
+namespace {
+
+// Picks the kernel for one GEMM on device pointers.  Returns launches made or a negative ACCB_ERR_*.
+int dispatch_gemm(const GemmLaunch& g, const char** err)
+{
+    const accb_gemm_desc& d = g.d;
+    if (d.k == 0) return launch_gemm_simt(g, err);          // nothing to accumulate: epilogue of beta * C
+    if (d.compute == ACCB_COMPUTE_SIMT) return launch_gemm_simt(g, err);
+    if (d.compute == ACCB_COMPUTE_TENSOR) return launch_gemm_umma(g, false, err);
+    if (d.compute == ACCB_COMPUTE_TENSOR_2SM) return launch_gemm_umma(g, true, err);
+    // AUTO: fp32 inputs stay on the bit-faithful fp32 path; narrower inputs take the tensor cores when the
+    // layout allows it (CTA pairs as soon as there is more than one 128-row tile) and the SIMT kernel otherwise
+    const char* why = nullptr;
+    if (d.a_type != ACCB_F32 && gemm_umma_supported(g, &why)) return launch_gemm_umma(g, d.m > 128, err);
+    return launch_gemm_simt(g, err);
+}
+
+// Large host-pointer GEMM: rows of A / C are staged in chunks on two streams so that the host->device
+// copy of chunk i+1, the GEMM of chunk i and the device->host copy of chunk i-1 overlap (PCIe is full
+// duplex and the copies dwarf the GEMM).  Needs row-major A and C so that a row range is one byte range.
+int pipelined_host_gemm(DeviceState& s, GemmLaunch g, const void* a, const void* b, void* c, const float* bias,
+                        size_t ea, size_t ec, size_t bytes_b)
+{
+    const accb_gemm_desc d = g.d;
+    cudaError_t e = cudaSuccess;
+    for (int i = 0; i < 2 && e == cudaSuccess; ++i)
+        if (!s.pipe[i]) e = cudaStreamCreateWithFlags(&s.pipe[i], cudaStreamNonBlocking);
+    if (e == cudaSuccess && !s.pipe_ready) e = cudaEventCreateWithFlags(&s.pipe_ready, cudaEventDisableTiming);
+    if (e != cudaSuccess) return fail_cuda("creating the staging pipeline", e);
+
+    int64_t chunk = (d.m + 7) / 8;
+    chunk = (chunk + 255) / 256 * 256;
+    if (chunk < 1024) chunk = 1024;
+
+    e = cudaMemcpyAsync(s.slot[1], b, bytes_b, cudaMemcpyHostToDevice, s.pipe[0]);
+    if (e == cudaSuccess && bias) e = cudaMemcpyAsync(s.slot[3], bias, (size_t)d.n * 4, cudaMemcpyHostToDevice, s.pipe[0]);
+    if (e == cudaSuccess) e = cudaEventRecord(s.pipe_ready, s.pipe[0]);
+    if (e != cudaSuccess) return fail_cuda("host to device copy", e);
+    g.b = s.slot[1];
+    g.bias = bias ? (const float*)s.slot[3] : nullptr;
+
+    int idx = 0;
+    for (int64_t r0 = 0; r0 < d.m; r0 += chunk, ++idx) {
+        const int64_t rows = (d.m - r0 < chunk) ? d.m - r0 : chunk;
+        cudaStream_t st = s.pipe[idx & 1];
+        const size_t off_a = (size_t)r0 * d.a_stride[0] * ea, len_a = ((size_t)(rows - 1) * d.a_stride[0] + d.k) * ea;
+        const size_t off_c = (size_t)r0 * d.c_stride[0] * ec, len_c = ((size_t)(rows - 1) * d.c_stride[0] + d.n) * ec;
+        if (idx & 1) e = cudaStreamWaitEvent(st, s.pipe_ready, 0);
+        if (e == cudaSuccess) e = cudaMemcpyAsync((char*)s.slot[0] + off_a, (const char*)a + off_a, len_a, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess && d.beta != 0.0f)
+            e = cudaMemcpyAsync((char*)s.slot[2] + off_c, (const char*)c + off_c, len_c, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return fail_cuda("host to device copy", e);
+        GemmLaunch part = g;
+        part.d.m = rows;
+        part.a = (const char*)s.slot[0] + off_a;
+        part.c = (char*)s.slot[2] + off_c;
+        part.stream = st;
+        const char* err = "";
+        const int n = dispatch_gemm(part, &err);
+        if (n < 0) {
+            cudaStreamSynchronize(s.pipe[0]);
+            cudaStreamSynchronize(s.pipe[1]);
+            return fail(n, std::string("accb_gemm: ") + err);
+        }
+        e = cudaMemcpyAsync((char*)c + off_c, (char*)s.slot[2] + off_c, len_c, cudaMemcpyDeviceToHost, st);
+        if (e != cudaSuccess) return fail_cuda("device to host copy", e);
+    }
+    e = cudaStreamSynchronize(s.pipe[0]);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s.pipe[1]);
+    if (e != cudaSuccess) return fail_cuda("kernel execution", e);
+    return collect_status(s, s.pipe[0]);
+}
+
+}  // namespace
+
 }  // namespace accb
 
 using namespace accb;
@@ -222,6 +299,9 @@ int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c,
         if ((rc = ensure(&s.slot[1], &s.slot_bytes[1], bytes_b)) != ACCB_OK) return rc;
         if ((rc = ensure(&s.slot[2], &s.slot_bytes[2], bytes_c)) != ACCB_OK) return rc;
         if (bias && (rc = ensure(&s.slot[3], &s.slot_bytes[3], (size_t)d.n * 4)) != ACCB_OK) return rc;
+        const bool row_major_ac = d.a_stride[1] == 1 && d.c_stride[1] == 1 && d.a_stride[0] >= d.k && d.c_stride[0] >= d.n;
+        if (row_major_ac && d.m >= 4096 && d.k > 0 && bytes_a + bytes_c >= ((size_t)64 << 20))
+            return pipelined_host_gemm(s, g, a, b, c, bias, ea, ec, bytes_b);
         cudaError_t e = cudaSuccess;
         if (bytes_a) e = cudaMemcpyAsync(s.slot[0], a, bytes_a, cudaMemcpyHostToDevice, g.stream);
         if (e == cudaSuccess && bytes_b) e = cudaMemcpyAsync(s.slot[1], b, bytes_b, cudaMemcpyHostToDevice, g.stream);
@@ -234,21 +314,7 @@ int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c,
     }
 
     const char* err = "";
-    int n;
-    if (d.k == 0) {
-        // nothing to accumulate: the SIMT kernel applies the epilogue to beta * C
-        n = launch_gemm_simt(g, &err);
-    } else if (d.compute == ACCB_COMPUTE_SIMT) {
-        n = launch_gemm_simt(g, &err);
-    } else if (d.compute == ACCB_COMPUTE_TENSOR || d.compute == ACCB_COMPUTE_TENSOR_2SM) {
-        n = launch_gemm_umma(g, d.compute == ACCB_COMPUTE_TENSOR_2SM, &err);
-    } else {
-        // AUTO: fp32 inputs stay on the bit-faithful fp32 path; narrower inputs take the
-        // tensor cores when the layout allows it and the SIMT kernel otherwise
-        const char* why = nullptr;
-        if (d.a_type != ACCB_F32 && gemm_umma_supported(g, &why)) n = launch_gemm_umma(g, false, &err);
-        else n = launch_gemm_simt(g, &err);
-    }
+    const int n = dispatch_gemm(g, &err);
     if (n < 0) return fail(n, std::string("accb_gemm: ") + err);
 
     if (all_host) {

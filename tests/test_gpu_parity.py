@@ -462,3 +462,30 @@ def test_golden_gather():
             got = np.empty_like(want)
             rt.gather_rank2(data, idx, got, axis)
             assert got.tobytes() == want.tobytes(), (name, axis)
+
+
+def test_large_host_buffers_take_the_pipelined_staging_path():
+    # >= 4096 rows and >= 64 MiB of A + C: rows are staged in chunks on two streams; the result must be the
+    # same as one launch on device-resident buffers, and right against the oracle on sampled rows
+    import torch
+    m, n, k = 8192 + 300, 2048, 4096           # ragged last chunk
+    A, B, C = oracle.inputs_gemm_bf16(m, n, k, seed=77)
+    rng = np.random.default_rng(78)
+    C0 = oracle.f32_to_bf16_bits(rng.standard_normal((m, n), dtype=np.float32))
+    got = C0.copy()
+    rt.set_stream(0)
+    rt.gemm(A, B, got, relu=True, kind="bfloat16", out_kind="bfloat16")
+    dev = torch.device("cuda:0")
+    At = torch.from_numpy(A.view(np.int16)).to(dev).view(torch.bfloat16)
+    Bt = torch.from_numpy(np.ascontiguousarray(B.T).view(np.int16)).to(dev).view(torch.bfloat16).t()
+    Ct = torch.from_numpy(C0.view(np.int16).copy()).to(dev).view(torch.bfloat16)
+    rt.gemm(At, Bt, Ct, relu=True, compute="tensor_2sm")
+    rt.synchronize()
+    ref_dev = Ct.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, ref_dev)
+    for r0 in (0, 1023, 1024, 5000, m - 9):
+        want = oracle.gemm(A, B, C0.copy(), in_kind="bfloat16", out_kind="bfloat16", relu=True, rows=(r0, r0 + 9))
+        a64 = oracle.bf16_bits_to_f32(A[r0:r0 + 9]).astype(np.float64)
+        scale = np.abs(a64) @ np.abs(oracle.bf16_bits_to_f32(B).astype(np.float64)) + np.abs(oracle.bf16_bits_to_f32(C0[r0:r0 + 9]))
+        _assert_close(oracle.bf16_bits_to_f32(got[r0:r0 + 9]), oracle.bf16_bits_to_f32(want[r0:r0 + 9]), scale, 1e-2,
+                      f"pipelined host path rows {r0}")
