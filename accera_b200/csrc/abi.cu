@@ -182,6 +182,11 @@ int dispatch_gemm(const GemmLaunch& g, const char** err)
     if (d.compute == ACCB_COMPUTE_SIMT) return launch_gemm_simt(g, err);
     if (d.compute == ACCB_COMPUTE_TENSOR) return launch_gemm_umma(g, false, err);
     if (d.compute == ACCB_COMPUTE_TENSOR_2SM) return launch_gemm_umma(g, true, err);
+    if (d.compute == ACCB_COMPUTE_TENSOR_PREFERRED) {
+        const char* why = nullptr;
+        if (gemm_umma_supported(g, &why)) return launch_gemm_umma(g, d.m > 128, err);
+        return launch_gemm_simt(g, err);
+    }
     // AUTO: fp32 inputs stay on the bit-faithful fp32 path; narrower inputs take the tensor cores when the
     // layout allows it (CTA pairs as soon as there is more than one 128-row tile) and the SIMT kernel otherwise
     const char* why = nullptr;
@@ -265,7 +270,7 @@ int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c,
         if (d.a_stride[i] < 1 || d.b_stride[i] < 1 || d.c_stride[i] < 1)
             return fail(ACCB_ERR_ARG, "accb_gemm: strides must be positive");
     if (d.epilogue != ACCB_EPI_NONE && d.epilogue != ACCB_EPI_RELU) return fail(ACCB_ERR_ARG, "accb_gemm: unknown epilogue");
-    if (d.compute < ACCB_COMPUTE_AUTO || d.compute > ACCB_COMPUTE_TENSOR_2SM) return fail(ACCB_ERR_ARG, "accb_gemm: unknown compute mode");
+    if (d.compute < ACCB_COMPUTE_AUTO || d.compute > ACCB_COMPUTE_TENSOR_PREFERRED) return fail(ACCB_ERR_ARG, "accb_gemm: unknown compute mode");
     if (d.m == 0 || d.n == 0) return ACCB_OK;
     if (!a || !b || !c) return fail(ACCB_ERR_ARG, "accb_gemm: null array pointer");
 

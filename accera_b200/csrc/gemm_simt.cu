@@ -177,6 +177,164 @@ gemm_simt_kernel(const TA* __restrict__ A, const TB* __restrict__ B, TC* __restr
     }
 }
 
+// ---------------------------------------------------------------------------------
+// fp32, row-major A / B / C: the quickstart layout.  Same arithmetic (fp32 FMA, k in
+// order inside a thread) but operands reach shared memory through a multi-stage
+// cp.async pipeline (16-byte copies, zero-filled at the ragged edges), so global-
+// memory latency is paid once in the prologue instead of once per k tile - at
+// 512^3 the kernel is otherwise bound by exactly that latency.
+// ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, int src_bytes)
+{
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int BM, int BN, int BK, int TM, int TN, int STAGES>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_simt_f32_rr_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                        const float* __restrict__ bias, SimtParams p)
+{
+    constexpr int NT = (BM / TM) * (BN / TN);
+    constexpr int LDA_S = BK + 4;                  // floats per A row in shared memory (16-byte aligned, conflict-free)
+    constexpr int LDB_S = BN + 4;
+    constexpr int A_STAGE = BM * LDA_S, B_STAGE = BK * LDB_S;
+    constexpr int A_CHUNKS = BM * BK / 4, B_CHUNKS = BK * BN / 4;
+    static_assert(TN == 4 && BK % 4 == 0, "thread tile is 4 columns wide; k tiles are whole 16-byte chunks");
+    static_assert(A_CHUNKS % NT == 0 || A_CHUNKS < NT, "A chunks must divide over the threads");
+    static_assert(B_CHUNKS % NT == 0, "B chunks must divide over the threads");
+    extern __shared__ __align__(16) float smem_f[];
+    float* As = smem_f;
+    float* Bs = smem_f + STAGES * A_STAGE;
+
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN);
+    const int ty = tid / (BN / TN);
+    const int64_t m0 = (int64_t)blockIdx.y * BM;
+    const int64_t n0 = (int64_t)blockIdx.x * BN;
+    const int64_t kt_count = (p.k + BK - 1) / BK;
+
+    auto load_stage = [&](int stage, int64_t kt) {
+        const int64_t k0 = kt * BK;
+#pragma unroll
+        for (int c = tid; c < A_CHUNKS; c += NT) {
+            const int r = c / (BK / 4), kc = (c % (BK / 4)) * 4;
+            const int64_t gm = m0 + r, gk = k0 + kc;
+            int bytes = 0;
+            if (gm < p.m && gk < p.k) bytes = (int)((p.k - gk >= 4 ? 4 : p.k - gk) * 4);
+            const float* src = bytes ? A + gm * p.as0 + gk : A;
+            cp_async16(As + stage * A_STAGE + r * LDA_S + kc, src, bytes);
+        }
+#pragma unroll
+        for (int c = tid; c < B_CHUNKS; c += NT) {
+            const int r = c / (BN / 4), nc = (c % (BN / 4)) * 4;
+            const int64_t gk = k0 + r, gn = n0 + nc;
+            int bytes = 0;
+            if (gk < p.k && gn < p.n) bytes = (int)((p.n - gn >= 4 ? 4 : p.n - gn) * 4);
+            const float* src = bytes ? B + gk * p.bs0 + gn : B;
+            cp_async16(Bs + stage * B_STAGE + r * LDB_S + nc, src, bytes);
+        }
+    };
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < kt_count) load_stage(s, s);
+        cp_async_commit();
+    }
+    for (int64_t kt = 0; kt < kt_count; ++kt) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();                       // tile kt has landed; tile kt-1's buffer is free again
+        if (kt + STAGES - 1 < kt_count) load_stage((int)((kt + STAGES - 1) % STAGES), kt + STAGES - 1);
+        cp_async_commit();
+        const float* as = As + (kt % STAGES) * A_STAGE + (ty * TM) * LDA_S;
+        const float* bs = Bs + (kt % STAGES) * B_STAGE + tx * TN;
+#pragma unroll
+        for (int kk = 0; kk < BK; kk += 4) {
+            float4 av[TM];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) av[i] = *reinterpret_cast<const float4*>(as + i * LDA_S + kk);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 bv = *reinterpret_cast<const float4*>(bs + (kk + q) * LDB_S);
+#pragma unroll
+                for (int i = 0; i < TM; ++i) {
+                    const float a = q == 0 ? av[i].x : q == 1 ? av[i].y : q == 2 ? av[i].z : av[i].w;
+                    acc[i][0] += a * bv.x; acc[i][1] += a * bv.y; acc[i][2] += a * bv.z; acc[i][3] += a * bv.w;
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    const bool c_vec = (p.cs0 % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int64_t gm = m0 + ty * TM + i;
+        if (gm >= p.m) continue;
+        const int64_t gn = n0 + tx * TN;
+        if (gn >= p.n) continue;
+        float* dst = C + gm * p.cs0 + gn;
+        float v[4] = { acc[i][0], acc[i][1], acc[i][2], acc[i][3] };
+        const int ncols = (int)(p.n - gn >= 4 ? 4 : p.n - gn);
+        float old[4] = { 0.f, 0.f, 0.f, 0.f };
+        if (p.beta != 0.0f) {
+            if (c_vec && ncols == 4) { const float4 o = *reinterpret_cast<const float4*>(dst); old[0] = o.x; old[1] = o.y; old[2] = o.z; old[3] = o.w; }
+            else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) if (j < ncols) old[j] = dst[j];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float x = v[j];
+            if (p.alpha == 1.0f) {
+                if (p.beta == 1.0f) x += old[j];
+                else if (p.beta != 0.0f) x += p.beta * old[j];
+            } else {
+                x *= p.alpha;
+                if (p.beta != 0.0f) x += p.beta * old[j];
+            }
+            if (bias && j < ncols) x += bias[gn + j];
+            if (p.relu) x = fmaxf(x, 0.0f);
+            v[j] = x;
+        }
+        if (c_vec && ncols == 4) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) if (j < ncols) dst[j] = v[j];
+        }
+    }
+}
+
+template <int BM, int BN, int BK, int TM, int TN, int STAGES>
+cudaError_t launch_f32_rr(const GemmLaunch& g, const SimtParams& p)
+{
+    constexpr int NT = (BM / TM) * (BN / TN);
+    constexpr size_t smem = (size_t)STAGES * (BM * (BK + 4) + BK * (BN + 4)) * sizeof(float);
+    auto kernel = gemm_simt_f32_rr_kernel<BM, BN, BK, TM, TN, STAGES>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)((p.m + BM - 1) / BM));
+    kernel<<<grid, NT, smem, g.stream>>>((const float*)g.a, (const float*)g.b, (float*)g.c, g.bias, p);
+    return cudaGetLastError();
+}
+
+// true when the cp.async kernel can take the problem: unit-stride rows, 16-byte aligned row starts
+bool f32_rr_ok(const GemmLaunch& g, const SimtParams& p)
+{
+    return p.as1 == 1 && p.bs1 == 1 && p.cs1 == 1 && p.as0 % 4 == 0 && p.bs0 % 4 == 0 &&
+           (reinterpret_cast<uintptr_t>(g.a) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.b) & 15) == 0 && p.k > 0;
+}
+
 template <typename TA, typename TB, typename TC, typename ACC>
 cudaError_t launch_typed(const GemmLaunch& g, const SimtParams& p)
 {
@@ -212,7 +370,15 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err)
 
     cudaError_t e;
     const int a = d.a_type, b = d.b_type, c = d.c_type;
-    if (a == ACCB_F32 && b == ACCB_F32 && c == ACCB_F32) e = launch_typed<float, float, float, float>(g, p);
+    if (a == ACCB_F32 && b == ACCB_F32 && c == ACCB_F32) {
+        if (f32_rr_ok(g, p)) {
+            const int64_t tiles64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
+            if (tiles64 >= 2 * (int64_t)g.num_sms) e = launch_f32_rr<64, 64, 32, 4, 4, 3>(g, p);
+            else e = launch_f32_rr<32, 64, 32, 2, 4, 4>(g, p);       // small problems: more, smaller tiles
+        } else {
+            e = launch_typed<float, float, float, float>(g, p);
+        }
+    }
     else if (a == ACCB_F16 && b == ACCB_F16 && c == ACCB_F32) e = launch_typed<__half, __half, float, float>(g, p);
     else if (a == ACCB_F16 && b == ACCB_F16 && c == ACCB_F16) e = launch_typed<__half, __half, __half, float>(g, p);
     else if (a == ACCB_BF16 && b == ACCB_BF16 && c == ACCB_F32) e = launch_typed<__nv_bfloat16, __nv_bfloat16, float, float>(g, p);

@@ -38,6 +38,7 @@
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <type_traits>
 
 #include "accb_internal.h"
@@ -77,6 +78,8 @@ struct UmmaParams {
     int elem_bytes;         // bytes per A/B element
     int tiles_m, tiles_n;   // tiles_m counts units of 128 rows (1 CTA) or 256 rows (pair)
     int group_m;            // tile rows visited together (L2 reuse)
+    int hint_a, hint_b;     // L2 eviction priority of the operand loads: 0 normal, 1 evict-first, 2 evict-last
+    int c_stream;           // read / write C with streaming (evict-first) accesses
     int* status;
 };
 
@@ -130,19 +133,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     return mbar_wait_slow(bar, parity, status, site, detail);
 }
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1)
+__device__ __forceinline__ uint64_t make_l2_policy(int hint)
+{
+    uint64_t pol;
+    if (hint == 1) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    else if (hint == 2) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    else asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, uint64_t pol)
 {
     asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "l"(pol)
         : "memory");
 }
 // CTA-pair form: the transaction bytes are signalled on the barrier of the pair's rank-0 CTA
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, uint64_t pol)
 {
     asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & kPeerMask), "r"(c0), "r"(c1)
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & kPeerMask), "r"(c0), "r"(c1), "l"(pol)
         : "memory");
 }
 
@@ -243,7 +255,9 @@ __device__ __forceinline__ void tile_coords(int t, const UmmaParams& p, int& tm,
     tn = in / rows;
 }
 
-template <typename TC> struct OutVec;   // 32 consecutive output elements of one row
+// 16-byte C accesses, optionally streaming (evict-first) so that C does not displace A / B panels in L2
+template <typename V> __device__ __forceinline__ V ld_c(const V* p, bool stream) { return stream ? __ldcs(p) : *p; }
+template <typename V> __device__ __forceinline__ void st_c(V* p, const V& v, bool stream) { if (stream) __stcs(p, v); else *p = v; }
 
 template <typename TC, typename ACC>
 __device__ __forceinline__ void epilogue_row(const uint32_t (&acc)[32], TC* __restrict__ crow, int64_t col0, int ncols,
@@ -260,7 +274,7 @@ __device__ __forceinline__ void epilogue_row(const uint32_t (&acc)[32], TC* __re
             if (p.beta != 0.0f) {
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
-                    int4 o = dst[q];
+                    int4 o = ld_c(dst + q, p.c_stream);
                     v[4 * q] += o.x; v[4 * q + 1] += o.y; v[4 * q + 2] += o.z; v[4 * q + 3] += o.w;
                 }
             }
@@ -269,7 +283,7 @@ __device__ __forceinline__ void epilogue_row(const uint32_t (&acc)[32], TC* __re
                 for (int j = 0; j < 32; ++j) v[j] = max(v[j], 0);
             }
 #pragma unroll
-            for (int q = 0; q < 8; ++q) dst[q] = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            for (int q = 0; q < 8; ++q) st_c(dst + q, make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]), p.c_stream);
         } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -296,7 +310,7 @@ __device__ __forceinline__ void epilogue_row(const uint32_t (&acc)[32], TC* __re
                 if (p.beta != 0.0f) {
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
-                        float4 o = dst[q];
+                        float4 o = ld_c(dst + q, p.c_stream);
                         v[4 * q] += p.beta * o.x; v[4 * q + 1] += p.beta * o.y;
                         v[4 * q + 2] += p.beta * o.z; v[4 * q + 3] += p.beta * o.w;
                     }
@@ -310,14 +324,14 @@ __device__ __forceinline__ void epilogue_row(const uint32_t (&acc)[32], TC* __re
                     for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
                 }
 #pragma unroll
-                for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                for (int q = 0; q < 8; ++q) st_c(dst + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]), p.c_stream);
             } else {
                 // 16-bit outputs: 8 elements per 16-byte vector
                 uint4* dst = reinterpret_cast<uint4*>(crow + col0);
                 if (p.beta != 0.0f) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        uint4 o = dst[q];
+                        uint4 o = ld_c(dst + q, p.c_stream);
                         const TC* h = reinterpret_cast<const TC*>(&o);
 #pragma unroll
                         for (int e = 0; e < 8; ++e) v[8 * q + e] += p.beta * (float)h[e];
@@ -337,7 +351,7 @@ __device__ __forceinline__ void epilogue_row(const uint32_t (&acc)[32], TC* __re
                     TC* h = reinterpret_cast<TC*>(&o);
 #pragma unroll
                     for (int e = 0; e < 8; ++e) h[e] = (TC)v[8 * q + e];
-                    dst[q] = o;
+                    st_c(dst + q, o, p.c_stream);
                 }
             }
         } else {
@@ -421,6 +435,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            const uint64_t pol_a = make_l2_policy(p.hint_a), pol_b = make_l2_policy(p.hint_b);
             for (int t = unit; t < num_tiles && ok; t += num_units) {
                 int tm, tn;
                 tile_coords(t, p, tm, tn);
@@ -434,12 +449,12 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint32_t sb = sa + Plan::kABytes;
                     if constexpr (TWO_SM) {
                         if (leader) mbar_arrive_expect_tx(full_bar(s), 2u * Plan::kStageBytes);
-                        tma_load_2d_pair(sa, &map_a, full_bar(s), kb * slab_elems, row_a);
-                        tma_load_2d_pair(sb, &map_b, full_bar(s), kb * slab_elems, row_b);
+                        tma_load_2d_pair(sa, &map_a, full_bar(s), kb * slab_elems, row_a, pol_a);
+                        tma_load_2d_pair(sb, &map_b, full_bar(s), kb * slab_elems, row_b, pol_b);
                     } else {
                         mbar_arrive_expect_tx(full_bar(s), (uint32_t)Plan::kStageBytes);
-                        tma_load_2d(sa, &map_a, full_bar(s), kb * slab_elems, row_a);
-                        tma_load_2d(sb, &map_b, full_bar(s), kb * slab_elems, row_b);
+                        tma_load_2d(sa, &map_a, full_bar(s), kb * slab_elems, row_a, pol_a);
+                        tma_load_2d(sb, &map_b, full_bar(s), kb * slab_elems, row_b, pol_b);
                     }
                 }
             }
@@ -682,6 +697,18 @@ int launch_gemm_umma(const GemmLaunch& g, bool two_sm, const char** err)
     p.tiles_m = (int)((d.m + rows_per_unit - 1) / rows_per_unit);
     p.tiles_n = (int)((d.n + kBlockN - 1) / kBlockN);
     p.group_m = two_sm ? 8 : 16;
+    p.hint_a = 0; p.hint_b = 0; p.c_stream = 0;
+    if (const char* tune = getenv("ACCB_GEMM_TUNE")) {
+        // tuning override for experiments: "g=<group_m>,a=<0|1|2>,b=<0|1|2>,c=<0|1>"
+        for (const char* q = tune; *q; ++q) {
+            if (q[1] != '=') continue;
+            const int v = atoi(q + 2);
+            if (*q == 'g' && v > 0) p.group_m = v;
+            else if (*q == 'a') p.hint_a = v;
+            else if (*q == 'b') p.hint_b = v;
+            else if (*q == 'c') p.c_stream = v;
+        }
+    }
     p.status = g.status;
     if ((int64_t)p.tiles_m * p.tiles_n > 0x3fffffff) { *err = "tcgen05 GEMM: too many tiles"; return ACCB_ERR_ARG; }
 

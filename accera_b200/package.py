@@ -33,7 +33,7 @@ _INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
 
 _ACCB_TYPE = {ScalarType.float32: "ACCB_F32", ScalarType.float16: "ACCB_F16", ScalarType.bfloat16: "ACCB_BF16",
               ScalarType.int8: "ACCB_S8", ScalarType.int32: "ACCB_S32", ScalarType.uint8: "ACCB_U8"}
-_COMPUTE = {"auto": "ACCB_COMPUTE_AUTO", "simt": "ACCB_COMPUTE_SIMT", "tensor": "ACCB_COMPUTE_TENSOR"}
+_COMPUTE = {"auto": "ACCB_COMPUTE_AUTO", "simt": "ACCB_COMPUTE_SIMT", "tensor": "ACCB_COMPUTE_TENSOR_PREFERRED"}
 
 
 class _PackagedFunction:
@@ -265,6 +265,16 @@ class Package:
                                     auxiliary=dict(fn.auxiliary))
             hfn.auxiliary["accera_b200"] = self._kernel_metadata(fn)
             hf.functions.append(hfn)
+            if fn.target.category is Target.Category.GPU and fn.spec.kind == "gemm" and fn.spec.compute == "tensor":
+                # GPU targets: the host entry names the kernel it launches and a device-function entry carries
+                # the launch geometry (Package.py:726-743); here that kernel is the persistent tcgen05 GEMM
+                # precompiled in the core library: one 192-thread CTA per SM, ~193 KiB of dynamic shared memory
+                hfn.launches = fn.name + "__gpu__"
+                hfn.runtime = "CUDA"
+                hf.device_functions.append(hat_file.Function(
+                    name=fn.name + "__gpu__", description="", calling_convention="device",
+                    arguments=[self._parameter(fn, a) for a in fn.args], launch_parameters=[148, 1, 1, 192, 1, 1],
+                    dynamic_shared_mem_bytes=197888, provider="libaccera_b200.so", runtime="CUDA"))
             decl.append(hfn.c_declaration() + "\n\n")
             if fn.base_name and fn.base_name not in seen_alias:
                 seen_alias.add(fn.base_name)

@@ -21,13 +21,14 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libaccera_b200.so")
 
 F32, F16, BF16, S8, S32, U8 = 0, 1, 2, 3, 4, 5
-COMPUTE_AUTO, COMPUTE_SIMT, COMPUTE_TENSOR, COMPUTE_TENSOR_2SM = 0, 1, 2, 3
+COMPUTE_AUTO, COMPUTE_SIMT, COMPUTE_TENSOR, COMPUTE_TENSOR_2SM, COMPUTE_TENSOR_PREFERRED = 0, 1, 2, 3, 4
 EPI_NONE, EPI_RELU = 0, 1
 ERR_ARG, ERR_CUDA, ERR_INDEX, ERR_TIMEOUT, ERR_LIMIT = -1, -2, -3, -4, -5
 
 TYPE_BYTES = {F32: 4, F16: 2, BF16: 2, S8: 1, S32: 4, U8: 1}
 _NP_TYPE = {"float32": F32, "float16": F16, "int8": S8, "int32": S32, "uint8": U8}
-_COMPUTE = {"auto": COMPUTE_AUTO, "simt": COMPUTE_SIMT, "tensor": COMPUTE_TENSOR, "tensor_2sm": COMPUTE_TENSOR_2SM}
+_COMPUTE = {"auto": COMPUTE_AUTO, "simt": COMPUTE_SIMT, "tensor": COMPUTE_TENSOR, "tensor_2sm": COMPUTE_TENSOR_2SM,
+            "tensor_preferred": COMPUTE_TENSOR_PREFERRED}
 
 EXPORTED_SYMBOLS = (
     "accb_gemm", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_noalloc", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",

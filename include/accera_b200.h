@@ -44,7 +44,10 @@ enum {
     ACCB_COMPUTE_AUTO = 0,   /* tensor cores for f16/bf16/s8/u8 inputs, fp32 SIMT for f32 inputs */
     ACCB_COMPUTE_SIMT = 1,   /* CUDA-core FMA in fp32 / int32: bit-faithful fp32 */
     ACCB_COMPUTE_TENSOR = 2, /* tcgen05: f16/bf16 -> f32, s8/u8 -> s32, f32 inputs as TF32 */
-    ACCB_COMPUTE_TENSOR_2SM = 3 /* tcgen05 with CTA pairs (cta_group::2); same numerics as TENSOR */
+    ACCB_COMPUTE_TENSOR_2SM = 3, /* tcgen05 with CTA pairs (cta_group::2); same numerics as TENSOR */
+    ACCB_COMPUTE_TENSOR_PREFERRED = 4 /* tcgen05 when the operand layout allows it (K-contiguous A and B,
+                                         16-byte row pitch), otherwise the SIMT kernel: what a tensorized
+                                         plan asks for, whatever the array layouts are */
 };
 
 /* fused epilogue applied to the accumulator before it is stored

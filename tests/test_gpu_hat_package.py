@@ -88,3 +88,33 @@ def test_run_benchmark_reports_hatlib_fields(tmp_path):
     for r in rows:
         d = r.as_dict()
         assert d["function_name"].startswith("matmul_relu_fusion_") and 0 < d["min_of_means"] <= d["mean"]
+
+
+@pytest.mark.parametrize("a_layout,b_layout,c_layout", [("F", "C", "C"), ("C", "C", "F"), ("F", "F", "F")])
+def test_tensorized_plan_with_any_layout(tmp_path, a_layout, b_layout, c_layout):
+    # the reference tensorizes every FIRST/LAST_MAJOR combination (mfma_tests.py:2797-2894); here layouts the
+    # tcgen05 kernel cannot take directly still give the right answer (SIMT kernel)
+    lay = {"C": acc.Array.Layout.FIRST_MAJOR, "F": acc.Array.Layout.LAST_MAJOR}
+    m, n, k = 96, 80, 64
+    A = acc.Array(role=acc.Role.INPUT, element_type=acc.ScalarType.float16, shape=(m, k), layout=lay[a_layout])
+    B = acc.Array(role=acc.Role.INPUT, element_type=acc.ScalarType.float16, shape=(k, n), layout=lay[b_layout])
+    C = acc.Array(role=acc.Role.INPUT_OUTPUT, element_type=acc.ScalarType.float32, shape=(m, n), layout=lay[c_layout])
+    nest = acc.Nest((m, n, k))
+    i, j, kk = nest.get_indices()
+
+    @nest.iteration_logic
+    def _():
+        C[i, j] += A[i, kk] * B[kk, j]
+    plan = nest.create_schedule().create_plan(acc.Target(acc.Target.Model.NVIDIA_B200))
+    plan.tensorize(indices=(i, j, kk), mma_shape=acc.MMAShape.M16xN16xK16_B1, prologue_op=acc.MMAFragmentOp.SET,
+                   prologue_arg=0, epilogue_op=acc.MMAFragmentOp.SCALE, epilogue_arg=5.0)
+    pkg = acc.Package()
+    pkg.add(plan, args=(A, B, C), base_name="mm")
+    _, fns = hat.load(pkg.build("lay_pkg", output_dir=str(tmp_path))[0])
+    rng = np.random.default_rng(9)
+    a = np.asarray(rng.random((m, k)), dtype=np.float16, order=a_layout)
+    b = np.asarray(rng.random((k, n)), dtype=np.float16, order=b_layout)
+    c = np.asarray(rng.random((m, n)), dtype=np.float32, order=c_layout)
+    fns.mm(a, b, c)
+    want = 5.0 * (a.astype(np.float64) @ b.astype(np.float64))        # alpha = 5, beta = 0 (mfma_tests.py:194)
+    np.testing.assert_allclose(c, want, rtol=1e-3)

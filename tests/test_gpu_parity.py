@@ -483,9 +483,25 @@ def test_large_host_buffers_take_the_pipelined_staging_path():
     rt.synchronize()
     ref_dev = Ct.view(torch.int16).cpu().numpy().view(np.uint16)
     assert np.array_equal(got, ref_dev)
-    for r0 in (0, 1023, 1024, 5000, m - 9):
+    for r0 in (0, 1275, 1280, 5000, m - 9):       # 1275..1283 straddles the first chunk boundary (1280 rows)
         want = oracle.gemm(A, B, C0.copy(), in_kind="bfloat16", out_kind="bfloat16", relu=True, rows=(r0, r0 + 9))
         a64 = oracle.bf16_bits_to_f32(A[r0:r0 + 9]).astype(np.float64)
         scale = np.abs(a64) @ np.abs(oracle.bf16_bits_to_f32(B).astype(np.float64)) + np.abs(oracle.bf16_bits_to_f32(C0[r0:r0 + 9]))
         _assert_close(oracle.bf16_bits_to_f32(got[r0:r0 + 9]), oracle.bf16_bits_to_f32(want[r0:r0 + 9]), scale, 1e-2,
                       f"pipelined host path rows {r0}")
+
+
+@pytest.mark.parametrize("m,n,k,lda,ldb", [(123, 236, 344, 344, 236), (130, 70, 345, 348, 72), (1, 4, 1, 4, 4), (700, 900, 130, 132, 900)])
+def test_simt_f32_cp_async_path_ragged(m, n, k, lda, ldb):
+    # row-major operands with 16-byte aligned row pitches take the multi-stage cp.async kernel;
+    # pitches larger than the logical width and K not a multiple of 4 exercise its zero-filled edges
+    rng = np.random.default_rng(m + n + k)
+    Abig = rng.standard_normal((m, lda), dtype=np.float32)
+    Bbig = rng.standard_normal((k, ldb), dtype=np.float32)
+    A, B = Abig[:, :k], Bbig[:, :n]
+    C0 = rng.standard_normal((m, n), dtype=np.float32)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    want = oracle.gemm(np.ascontiguousarray(A), np.ascontiguousarray(B), C0.copy(), bias=bias, relu=True)
+    got = C0.copy()
+    rt.gemm(A, B, got, bias=bias, relu=True, compute="simt")
+    _assert_close(got, want, _gemm_scale(A, B) + np.abs(C0) + np.abs(bias), RTOL_F32, f"simt cp.async {m}x{n}x{k}")

@@ -379,3 +379,67 @@ def test_benchmark_statistics_fields():
     assert set(d) == {"function_name", "mean", "median_of_means", "mean_of_small_means", "robust_mean", "min_of_means"}
     assert d["min_of_means"] == 1.0 and d["median_of_means"] == 2.0 and d["mean"] == pytest.approx(3.5)
     assert d["robust_mean"] == pytest.approx((1.5 + 2.0 + 3.0) / 3)
+
+
+def test_runtime_sized_matmul_and_reduce_mean_packages(tmp_path):
+    # runtime-size matmul (dsl_tests.py:1051-1069 form): dimensions are int64 arguments, arrays are runtime_arrays
+    M, N, K = acc.create_dimensions()
+    A = acc.Array(role=acc.Role.INPUT, element_type=acc.ScalarType.float32, shape=(M, K))
+    B = acc.Array(role=acc.Role.INPUT, element_type=acc.ScalarType.float32, shape=(K, N))
+    C = acc.Array(role=acc.Role.INPUT_OUTPUT, element_type=acc.ScalarType.float32, shape=(M, N))
+    nest = acc.Nest((M, N, K))
+    i, j, k = nest.get_indices()
+
+    @nest.iteration_logic
+    def _():
+        C[i, j] += A[i, k] * B[k, j]
+    pkg = acc.Package()
+    pkg.add(nest, args=(A, B, C, M, N, K), base_name="matmul_dyn")
+    # runtime-size reduce_mean over the last axis of a rank-2 array
+    R, L = acc.create_dimensions()
+    data = acc.Array(role=acc.Role.INPUT, shape=(R, L))
+    red = acc.Array(role=acc.Role.INPUT_OUTPUT, shape=(R,))
+    n0 = acc.Nest((R,)); a0, = n0.get_indices()
+
+    @n0.iteration_logic
+    def _():
+        red[a0] = 0.0
+    n1 = acc.Nest((R, L)); r, c = n1.get_indices()
+
+    @n1.iteration_logic
+    def _():
+        red[r] += data[r, c]
+    n2 = acc.Nest((R,)); a2, = n2.get_indices()
+
+    @n2.iteration_logic
+    def _():
+        red[a2] /= acc.cast(L, acc.ScalarType.float32)
+    pkg.add(acc.fuse((n0, n1, n2), partial=1), args=(R, L, data, red), base_name="ReduceMean_dyn")
+    files = pkg.build("dyn_pkg", format=acc.Package.Format.HAT_DYNAMIC | acc.Package.Format.SOURCE, output_dir=str(tmp_path))
+    hf = hat.HATFile.read(files[0])
+    mm, rm = hf.functions
+    assert mm.c_declaration().endswith("(float*, float*, float*, int64_t, int64_t, int64_t);")
+    assert [a.logical_type for a in mm.arguments] == ["runtime_array"] * 3 + ["element"] * 3
+    assert mm.arguments[0].size == "M*K" and mm.arguments[2].size == "M*N" and mm.arguments[3].name == "M"
+    assert rm.c_declaration().endswith("(int64_t, int64_t, float*, float*);")
+    src = open([f for f in files if f.endswith(".cpp")][0]).read()
+    assert "d.m = a3; d.n = a4; d.k = a5;" in src and "d.a_stride[0] = a5;" in src and "d.c_stride[0] = a4;" in src
+    assert "accb_reduce_mean_rank3(a2, INT64_C(1), a0, a1, a3, 4)" in src
+
+
+def test_gpu_target_functions_list_their_device_kernel(tmp_path):
+    # the reference adds a device-function entry and a `launches` link for GPU targets (Package.py:726-743)
+    nest, args = _gemm_nest(512, 512, 512, acc.ScalarType.float16, acc.ScalarType.float32, acc.Layout.LAST_MAJOR)
+    plan = nest.create_schedule().create_plan(acc.Target(acc.Target.Model.NVIDIA_B200))
+    plan.tensorize(indices=tuple(nest.get_indices()), mma_shape=acc.MMAShape.M16xN16xK16_B1)
+    pkg = acc.Package()
+    fn = pkg.add(plan, args=args, base_name="mm_gpu")
+    hf = hat.HATFile.read(pkg.build("gpu_pkg", output_dir=str(tmp_path))[0])
+    host = hf.functions[0]
+    assert host.launches == fn.name + "__gpu__" and host.runtime == "CUDA"
+    dev = hf.device_functions[0]
+    assert dev.name == fn.name + "__gpu__" and dev.calling_convention == "device"
+    assert dev.launch_parameters[3:] == [192, 1, 1] and dev.dynamic_shared_mem_bytes > 190000
+    assert dev.provider == "libaccera_b200.so"
+    _, fns = hat.load(hf.path)
+    assert fns.names == [fn.name]                      # device functions are not host-callable
