@@ -16,6 +16,7 @@
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <type_traits>
 
 #include "accb_internal.h"
@@ -257,19 +258,35 @@ gemm_simt_f32_rr_kernel(const float* __restrict__ A, const float* __restrict__ B
         cp_async_commit();
         const float* as = As + (kt % STAGES) * A_STAGE + (ty * TM) * LDA_S;
         const float* bs = Bs + (kt % STAGES) * B_STAGE + tx * TN;
+        // register double buffering: the fragments of the next 4 k are loaded while the current 4 are used,
+        // so that shared-memory latency is covered even with two warps per scheduler
+        float4 a_cur[TM], b_cur[4], a_nxt[TM], b_nxt[4];
+#pragma unroll
+        for (int i = 0; i < TM; ++i) a_cur[i] = *reinterpret_cast<const float4*>(as + i * LDA_S);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) b_cur[q] = *reinterpret_cast<const float4*>(bs + q * LDB_S);
 #pragma unroll
         for (int kk = 0; kk < BK; kk += 4) {
-            float4 av[TM];
+            if (kk + 4 < BK) {
 #pragma unroll
-            for (int i = 0; i < TM; ++i) av[i] = *reinterpret_cast<const float4*>(as + i * LDA_S + kk);
+                for (int i = 0; i < TM; ++i) a_nxt[i] = *reinterpret_cast<const float4*>(as + i * LDA_S + kk + 4);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) b_nxt[q] = *reinterpret_cast<const float4*>(bs + (kk + 4 + q) * LDB_S);
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                const float4 bv = *reinterpret_cast<const float4*>(bs + (kk + q) * LDB_S);
+                const float4 bv = b_cur[q];
 #pragma unroll
                 for (int i = 0; i < TM; ++i) {
-                    const float a = q == 0 ? av[i].x : q == 1 ? av[i].y : q == 2 ? av[i].z : av[i].w;
+                    const float a = q == 0 ? a_cur[i].x : q == 1 ? a_cur[i].y : q == 2 ? a_cur[i].z : a_cur[i].w;
                     acc[i][0] += a * bv.x; acc[i][1] += a * bv.y; acc[i][2] += a * bv.z; acc[i][3] += a * bv.w;
                 }
+            }
+            if (kk + 4 < BK) {
+#pragma unroll
+                for (int i = 0; i < TM; ++i) a_cur[i] = a_nxt[i];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) b_cur[q] = b_nxt[q];
             }
         }
     }
@@ -373,7 +390,15 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err)
     if (a == ACCB_F32 && b == ACCB_F32 && c == ACCB_F32) {
         if (f32_rr_ok(g, p)) {
             const int64_t tiles64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
-            if (tiles64 >= 2 * (int64_t)g.num_sms) e = launch_f32_rr<64, 64, 32, 4, 4, 3>(g, p);
+            int variant = -1;
+            if (const char* v = getenv("ACCB_SIMT_VARIANT")) variant = atoi(v);     // experiments only
+            if (variant == 0) e = launch_f32_rr<32, 64, 32, 2, 4, 4>(g, p);
+            else if (variant == 1) e = launch_f32_rr<32, 64, 32, 4, 4, 4>(g, p);
+            else if (variant == 2) e = launch_f32_rr<32, 32, 32, 2, 4, 4>(g, p);
+            else if (variant == 3) e = launch_f32_rr<64, 64, 32, 4, 4, 3>(g, p);
+            else if (variant == 4) e = launch_f32_rr<16, 64, 32, 2, 4, 4>(g, p);
+            else if (variant == 5) e = launch_f32_rr<32, 64, 16, 2, 4, 6>(g, p);
+            else if (tiles64 >= 2 * (int64_t)g.num_sms) e = launch_f32_rr<64, 64, 32, 4, 4, 3>(g, p);
             else e = launch_f32_rr<32, 64, 32, 2, 4, 4>(g, p);       // small problems: more, smaller tiles
         } else {
             e = launch_typed<float, float, float, float>(g, p);

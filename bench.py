@@ -411,7 +411,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--compute", default="tensor_2sm", choices=["tensor", "tensor_2sm"])
-    ap.add_argument("--chunks", type=int, default=2, help="row-block rounds per rank for GEMM / all-gather overlap (N > 1)")
+    ap.add_argument("--chunks", type=int, default=4, help="row-block rounds per rank for GEMM / all-gather overlap (N > 1)")
     ap.add_argument("--no-extras", action="store_true", help="skip the device-timed numbers of the other configurations")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
