@@ -271,6 +271,7 @@ int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c,
             return fail(ACCB_ERR_ARG, "accb_gemm: strides must be positive");
     if (d.epilogue != ACCB_EPI_NONE && d.epilogue != ACCB_EPI_RELU) return fail(ACCB_ERR_ARG, "accb_gemm: unknown epilogue");
     if (d.compute < ACCB_COMPUTE_AUTO || d.compute > ACCB_COMPUTE_TENSOR_PREFERRED) return fail(ACCB_ERR_ARG, "accb_gemm: unknown compute mode");
+    if (d.max_ctas < 0) return fail(ACCB_ERR_ARG, "accb_gemm: max_ctas must be >= 0");
     if (d.m == 0 || d.n == 0) return ACCB_OK;
     if (!a || !b || !c) return fail(ACCB_ERR_ARG, "accb_gemm: null array pointer");
 
@@ -288,6 +289,7 @@ int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c,
 
     GemmLaunch g;
     g.d = d;
+    g.n_extra_c = 0;
     g.stream = t_stream;
     g.status = s.status;
     g.device = dev;
@@ -327,6 +329,42 @@ int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c,
         if (e != cudaSuccess) return fail_cuda("device to host copy", e);
         return collect_status(s, g.stream);
     }
+    return ACCB_OK;
+}
+
+int accb_gemm_replicated(const accb_gemm_desc* desc, const void* a, const void* b, void* const* c_replicas,
+                         int32_t n_replicas, const float* bias)
+{
+    t_error.clear();
+    if (!desc) return fail(ACCB_ERR_ARG, "accb_gemm_replicated: null descriptor");
+    if (!c_replicas || n_replicas < 1 || n_replicas > 8) return fail(ACCB_ERR_ARG, "accb_gemm_replicated: 1 to 8 replicas");
+    const accb_gemm_desc& d = *desc;
+    if (d.m <= 0 || d.n <= 0 || d.k <= 0) return fail(ACCB_ERR_ARG, "accb_gemm_replicated: dimensions must be positive");
+    if (!type_bytes(d.a_type) || !type_bytes(d.b_type) || !type_bytes(d.c_type)) return fail(ACCB_ERR_ARG, "accb_gemm_replicated: unknown element type");
+    for (int i = 0; i < 2; ++i)
+        if (d.a_stride[i] < 1 || d.b_stride[i] < 1 || d.c_stride[i] < 1)
+            return fail(ACCB_ERR_ARG, "accb_gemm_replicated: strides must be positive");
+    if (d.epilogue != ACCB_EPI_NONE && d.epilogue != ACCB_EPI_RELU) return fail(ACCB_ERR_ARG, "accb_gemm_replicated: unknown epilogue");
+    if (d.max_ctas < 0) return fail(ACCB_ERR_ARG, "accb_gemm_replicated: max_ctas must be >= 0");
+    if (!a || !b || !c_replicas[0]) return fail(ACCB_ERR_ARG, "accb_gemm_replicated: null array pointer");
+    DeviceState* sp = nullptr;
+    int dev = 0;
+    int rc = device_state(&sp, &dev);
+    if (rc != ACCB_OK) return rc;
+    if (!is_device_pointer(a) || !is_device_pointer(b) || !is_device_pointer(c_replicas[0]) || (bias && !is_device_pointer(bias)))
+        return fail(ACCB_ERR_ARG, "accb_gemm_replicated: device pointers only");
+    GemmLaunch g;
+    g.d = d;
+    g.a = a; g.b = b; g.c = c_replicas[0]; g.bias = bias;
+    g.n_extra_c = n_replicas - 1;
+    for (int r = 1; r < n_replicas; ++r) g.extra_c[r - 1] = c_replicas[r];
+    g.stream = t_stream;
+    g.status = sp->status;
+    g.device = dev;
+    g.num_sms = sp->num_sms;
+    const char* err = "";
+    const int n = launch_gemm_umma(g, d.compute != ACCB_COMPUTE_TENSOR, &err);
+    if (n < 0) return fail(n, std::string("accb_gemm_replicated: ") + err);
     return ACCB_OK;
 }
 

@@ -25,6 +25,10 @@ struct GemmLaunch {
     const void* b;
     void* c;
     const float* bias;
+    // additional destinations that receive the same result with the same layout (may be peer memory);
+    // only the tensor-core path with a TMA-storable C supports them
+    void* extra_c[7];
+    int n_extra_c;
     cudaStream_t stream;
     int* status;       // device pointer to kStatusWords ints
     int device;

@@ -39,6 +39,7 @@
 #include <cuda_bf16.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <type_traits>
 
 #include "accb_internal.h"
@@ -66,8 +67,14 @@ template <bool TWO_SM> struct SmemPlan {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = TWO_SM ? 6 : 4;
     static constexpr int kBarrierBytes = 256;
-    static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;   // +1024: manual alignment
+    // epilogue staging for TMA stores: per epilogue warp two boxes of 32 rows x 32 elements (<= 4 bytes each)
+    static constexpr int kStoreBoxBytes = 32 * 32 * 4;
+    static constexpr int kStoreBytes = kEpiWarps * 2 * kStoreBoxBytes;
+    static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + kStoreBytes + 1024;   // +1024: manual alignment
 };
+
+constexpr int kMaxReplicas = 8;
+struct CReplicaMaps { CUtensorMap m[kMaxReplicas]; };   // tensor maps of the C replicas (TMA-store epilogue)
 
 struct UmmaParams {
     int64_t m, n, k;
@@ -80,6 +87,8 @@ struct UmmaParams {
     int group_m;            // tile rows visited together (L2 reuse)
     int hint_a, hint_b;     // L2 eviction priority of the operand loads: 0 normal, 1 evict-first, 2 evict-last
     int c_stream;           // read / write C with streaming (evict-first) accesses
+    int tma_store;          // epilogue goes through shared memory and TMA stores (row-major C with 16-byte pitch)
+    int n_replicas;         // number of C replicas the result is stored to (1 = just C); replicas may be peer memory
     int* status;
 };
 
@@ -156,6 +165,13 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & kPeerMask), "r"(c0), "r"(c1), "l"(pol)
         : "memory");
+}
+
+// TMA store of one shared-memory box into a C replica (rows / columns outside the tensor are clipped)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1) : "memory");
 }
 
 // Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes
@@ -370,10 +386,108 @@ __device__ __forceinline__ void epilogue_row(const uint32_t (&acc)[32], TC* __re
     }
 }
 
+// Same arithmetic as epilogue_row, but the 32 results of this thread's row go to `srow` in shared memory
+// (the staging box of a TMA store).  C is only read (beta != 0) where it exists; values computed for
+// rows / columns outside the matrix are never stored, the TMA store clips them.
+template <typename TC, typename ACC>
+__device__ __forceinline__ void epilogue_to_smem(const uint32_t (&acc)[32], const TC* __restrict__ crow, bool row_ok,
+                                                 int64_t col0, int ncols, bool c_vec, const float* __restrict__ bias,
+                                                 const UmmaParams& p, TC* srow)
+{
+    const bool full = (ncols == 32);
+    if constexpr (std::is_same<ACC, int>::value) {
+        int v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (int)acc[j];
+        if (p.beta != 0.0f && row_ok) {
+            if (c_vec && full) {
+                const int4* src = reinterpret_cast<const int4*>(crow + col0);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const int4 o = ld_c(src + q, p.c_stream);
+                    v[4 * q] += o.x; v[4 * q + 1] += o.y; v[4 * q + 2] += o.z; v[4 * q + 3] += o.w;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += (int)crow[col0 + j];
+            }
+        }
+        if (p.relu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = max(v[j], 0);
+        }
+        int4* dst = reinterpret_cast<int4*>(srow);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) dst[q] = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    } else {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
+        if (p.alpha != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+        }
+        if (p.beta != 0.0f && row_ok) {
+            if (c_vec && full) {
+                if constexpr (sizeof(TC) == 4) {
+                    const float4* src = reinterpret_cast<const float4*>(crow + col0);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const float4 o = ld_c(src + q, p.c_stream);
+                        v[4 * q] += p.beta * o.x; v[4 * q + 1] += p.beta * o.y;
+                        v[4 * q + 2] += p.beta * o.z; v[4 * q + 3] += p.beta * o.w;
+                    }
+                } else {
+                    const uint4* src = reinterpret_cast<const uint4*>(crow + col0);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint4 o = ld_c(src + q, p.c_stream);
+                        const TC* h = reinterpret_cast<const TC*>(&o);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[8 * q + e] += p.beta * (float)h[e];
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += p.beta * (float)crow[col0 + j];
+            }
+        }
+        if (bias) {
+            if (full) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += __ldg(bias + col0 + j);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += __ldg(bias + col0 + j);
+            }
+        }
+        if (p.relu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+        }
+        if constexpr (sizeof(TC) == 4) {
+            float4* dst = reinterpret_cast<float4*>(srow);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        } else {
+            uint4* dst = reinterpret_cast<uint4*>(srow);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                TC* h = reinterpret_cast<TC*>(&o);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) h[e] = (TC)v[8 * q + e];
+                dst[q] = o;
+            }
+        }
+    }
+}
+
 template <int KIND, typename TC, bool TWO_SM>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 TC* __restrict__ C, const float* __restrict__ bias, const UmmaParams p)
+                 const __grid_constant__ CReplicaMaps cmaps, TC* __restrict__ C, const float* __restrict__ bias,
+                 const UmmaParams p)
 {
     using Plan = SmemPlan<TWO_SM>;
     using ACC = typename std::conditional<KIND == KIND_I8, int, float>::type;
@@ -499,6 +613,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                            ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
         int local = 0;
         bool ok = true;
+        uint32_t store_count = 0;                    // TMA-store boxes this warp has issued (warp-uniform)
+        uint8_t* store_stage = smem_gen + S * Plan::kStageBytes + Plan::kBarrierBytes +
+                               (size_t)(warp - 2) * 2 * Plan::kStoreBoxBytes;
         for (int t = unit; t < num_tiles && ok; t += num_units, ++local) {
             int tm, tn;
             tile_coords(t, p, tm, tn);
@@ -511,15 +628,37 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int64_t col_tile = (int64_t)tn * kBlockN;
             TC* crow = C + row * p.cs0;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kBlockN);
+            const int64_t row0 = (int64_t)(tm * kCtas + (int)rank) * kBlockM + q * 32;     // first row of this warp
 #pragma unroll 1
             for (int c = 0; c < kBlockN / 32; ++c) {
                 uint32_t acc[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), acc);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int64_t col0 = col_tile + c * 32;
-                if (row < p.m && col0 < p.n) {
+                if (!p.tma_store) {
+                    if (row < p.m && col0 < p.n) {
+                        const int ncols = (int)min((int64_t)32, p.n - col0);
+                        epilogue_row<TC, ACC>(acc, crow, col0, ncols, c_vec, p.cs1, bias, p);
+                    }
+                } else if (row0 < p.m && col0 < p.n) {        // warp-uniform: the box has something to store
                     const int ncols = (int)min((int64_t)32, p.n - col0);
-                    epilogue_row<TC, ACC>(acc, crow, col0, ncols, c_vec, p.cs1, bias, p);
+                    const int sb = (int)(store_count & 1u);
+                    // the box about to be overwritten was handed to TMA two chunks ago: wait until it has been read
+                    if (store_count >= 2) {
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        __syncwarp();
+                    }
+                    uint8_t* box = store_stage + (size_t)sb * Plan::kStoreBoxBytes;
+                    epilogue_to_smem<TC, ACC>(acc, crow, row < p.m, col0, ncols, c_vec, bias, p,
+                                              reinterpret_cast<TC*>(box) + lane * 32);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to TMA
+                    __syncwarp();
+                    if (lane == 0) {
+                        const uint32_t src = smem_u32(box);
+                        for (int r = 0; r < p.n_replicas; ++r) tma_store_2d(&cmaps.m[r], src, (int)col0, (int)row0);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    ++store_count;
                 }
             }
             // this warp has drained its part of the accumulator: hand it back to the MMA issuer
@@ -527,6 +666,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(TWO_SM ? (tmem_empty_bar(buf) & kPeerMask) : tmem_empty_bar(buf));
         }
+        // all TMA stores of this warp (also those into peer memory) must have completed before the CTA exits
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        __syncwarp();
     }
 
     // teardown: every role ends here, also after a bounded wait gave up
@@ -600,6 +742,34 @@ bool make_operand_map(CUtensorMap* map, const void* base, int type, int64_t rows
     return r == CUDA_SUCCESS;
 }
 
+// C (or a replica of it) as a row-major [m, n] tensor; box = 32 x 32 elements, no swizzle
+bool make_c_map(CUtensorMap* map, void* base, int type, int64_t m, int64_t n, int64_t ld)
+{
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return false;
+    CUtensorMapDataType dt;
+    switch (type) {
+    case ACCB_F16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+    case ACCB_BF16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
+    case ACCB_F32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
+    default: dt = CU_TENSOR_MAP_DATA_TYPE_INT32; break;
+    }
+    const int es = elem_size(type);
+    cuuint64_t dims[2] = { (cuuint64_t)n, (cuuint64_t)m };
+    cuuint64_t strides[1] = { (cuuint64_t)(ld * es) };
+    cuuint32_t box[2] = { 32, 32 };
+    cuuint32_t estr[2] = { 1, 1 };
+    CUresult r = enc(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+bool c_tma_storable(const accb_gemm_desc& d, const void* c)
+{
+    return d.c_stride[1] == 1 && (d.c_stride[0] * elem_size(d.c_type)) % 16 == 0 &&
+           (reinterpret_cast<uintptr_t>(c) & 15) == 0;
+}
+
 uint32_t make_idesc(int a_type, int b_type, bool int_acc, bool f16_out_acc, int m, int n)
 {
     auto fmt = [](int t) -> uint32_t {
@@ -619,7 +789,8 @@ uint32_t make_idesc(int a_type, int b_type, bool int_acc, bool f16_out_acc, int 
 }
 
 template <int KIND, typename TC, bool TWO_SM>
-int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap& mb, UmmaParams p, const char** err)
+int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap& mb, const CReplicaMaps& cm, UmmaParams p,
+                   const char** err)
 {
     using Plan = SmemPlan<TWO_SM>;
     auto kernel = gemm_umma_kernel<KIND, TC, TWO_SM>;
@@ -642,9 +813,13 @@ int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap
         if (e != cudaSuccess || max_clusters < 1) { *err = "tcgen05 GEMM: no CTA pair can be resident"; (void)cudaGetLastError(); return ACCB_ERR_CUDA; }
         units = max_clusters < g.num_sms / 2 ? max_clusters : g.num_sms / 2;
     }
+    if (g.d.max_ctas > 0) {
+        const int cap = g.d.max_ctas / (TWO_SM ? 2 : 1);
+        if (cap >= 1 && cap < units) units = cap;
+    }
     if (units > num_tiles) units = num_tiles;
     cfg.gridDim = dim3((unsigned)(units * (TWO_SM ? 2 : 1)));
-    e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, (TC*)g.c, g.bias, p);
+    e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, cm, (TC*)g.c, g.bias, p);
     if (e != cudaSuccess) { *err = cudaGetErrorString(e); return ACCB_ERR_CUDA; }
     note_launches(1);
     return 1;
@@ -698,6 +873,8 @@ int launch_gemm_umma(const GemmLaunch& g, bool two_sm, const char** err)
     p.tiles_n = (int)((d.n + kBlockN - 1) / kBlockN);
     p.group_m = two_sm ? 8 : 16;
     p.hint_a = 0; p.hint_b = 0; p.c_stream = 0;
+    p.tma_store = c_tma_storable(d, g.c) ? 1 : 0;
+    p.n_replicas = 1 + g.n_extra_c;
     if (const char* tune = getenv("ACCB_GEMM_TUNE")) {
         // tuning override for experiments: "g=<group_m>,a=<0|1|2>,b=<0|1|2>,c=<0|1>"
         for (const char* q = tune; *q; ++q) {
@@ -707,13 +884,26 @@ int launch_gemm_umma(const GemmLaunch& g, bool two_sm, const char** err)
             else if (*q == 'a') p.hint_a = v;
             else if (*q == 'b') p.hint_b = v;
             else if (*q == 'c') p.c_stream = v;
+            else if (*q == 't' && g.n_extra_c == 0) p.tma_store = v && p.tma_store;
         }
+    }
+    CReplicaMaps cm;
+    memset(&cm, 0, sizeof cm);
+    if (g.n_extra_c < 0 || g.n_extra_c > kMaxReplicas - 1) { *err = "tcgen05 GEMM: at most 7 extra C replicas"; return ACCB_ERR_ARG; }
+    if (g.n_extra_c > 0 && !p.tma_store) { *err = "tcgen05 GEMM: C replicas need a row-major C with a 16-byte aligned pitch and base"; return ACCB_ERR_ARG; }
+    if (p.tma_store) {
+        bool ok = make_c_map(&cm.m[0], g.c, d.c_type, d.m, d.n, d.c_stride[0]);
+        for (int r = 0; r < g.n_extra_c && ok; ++r) {
+            if (!g.extra_c[r] || (reinterpret_cast<uintptr_t>(g.extra_c[r]) & 15)) { *err = "tcgen05 GEMM: C replica pointers must be non-null and 16-byte aligned"; return ACCB_ERR_ARG; }
+            ok = make_c_map(&cm.m[1 + r], g.extra_c[r], d.c_type, d.m, d.n, d.c_stride[0]);
+        }
+        if (!ok) { *err = "tcgen05 GEMM: cuTensorMapEncodeTiled failed for C"; return ACCB_ERR_CUDA; }
     }
     p.status = g.status;
     if ((int64_t)p.tiles_m * p.tiles_n > 0x3fffffff) { *err = "tcgen05 GEMM: too many tiles"; return ACCB_ERR_ARG; }
 
 #define ACCB_UMMA_LAUNCH(KIND, TC)                                                          \
-    (two_sm ? launch_variant<KIND, TC, true>(g, ma, mb, p, err) : launch_variant<KIND, TC, false>(g, ma, mb, p, err))
+    (two_sm ? launch_variant<KIND, TC, true>(g, ma, mb, cm, p, err) : launch_variant<KIND, TC, false>(g, ma, mb, cm, p, err))
 
     if (d.a_type == ACCB_F16 || d.a_type == ACCB_BF16) {
         if (d.c_type == ACCB_F32) return ACCB_UMMA_LAUNCH(KIND_F16, float);

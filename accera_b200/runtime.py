@@ -31,7 +31,7 @@ _COMPUTE = {"auto": COMPUTE_AUTO, "simt": COMPUTE_SIMT, "tensor": COMPUTE_TENSOR
             "tensor_preferred": COMPUTE_TENSOR_PREFERRED}
 
 EXPORTED_SYMBOLS = (
-    "accb_gemm", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_noalloc", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
+    "accb_gemm", "accb_gemm_replicated", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_noalloc", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
     "accb_gather_rank2_dims", "accb_set_device", "accb_set_stream", "accb_synchronize", "accb_last_error",
     "accb_launch_count", "accb_release_workspace", "accb_device_count", "accb_version",
 )
@@ -52,7 +52,7 @@ class GemmDesc(ctypes.Structure):
         ("compute", ctypes.c_int32),
         ("a_stride", ctypes.c_int64 * 2), ("b_stride", ctypes.c_int64 * 2), ("c_stride", ctypes.c_int64 * 2),
         ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
-        ("epilogue", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("epilogue", ctypes.c_int32), ("max_ctas", ctypes.c_int32),
     ]
 
 
@@ -73,6 +73,8 @@ def lib() -> ctypes.CDLL:
     vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32
     L.accb_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp]
     L.accb_gemm.restype = ctypes.c_int
+    L.accb_gemm_replicated.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp), i32, vp]
+    L.accb_gemm_replicated.restype = ctypes.c_int
     L.accb_reduce_mean_rank3.argtypes = [vp, i64, i64, i64, vp, i32]
     L.accb_reduce_mean_rank3.restype = ctypes.c_int
     L.accb_reduce_mean_rank3_noalloc.argtypes = [vp, i64, i64, i64, vp, i32, vp]
@@ -193,12 +195,13 @@ def _sync_torch_stream(*arrays) -> None:
 # ---------------------------------------------------------------------------
 
 def gemm(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: bool = False, compute: str = "auto",
-         kind: Optional[str] = None, out_kind: Optional[str] = None) -> None:
+         kind: Optional[str] = None, out_kind: Optional[str] = None, max_ctas: int = 0) -> None:
     """C <- epi(alpha * A @ B + beta * C + bias), in place in C.
 
     A [M,K], B [K,N], C [M,N]; strides are taken from the arrays, so a Fortran-
     ordered B is the reference's LAST_MAJOR layout.  `kind`/`out_kind` = "bfloat16"
-    marks uint16 numpy arrays as bf16 bit patterns.
+    marks uint16 numpy arrays as bf16 bit patterns.  `max_ctas` bounds the tensor-core kernel's persistent
+    grid (0 = every SM), to leave SMs for a collective that runs concurrently.
     """
     pa, ta, sha, sta, da = _describe(A, kind)
     pb, tb, shb, stb, db = _describe(B, kind)
@@ -223,8 +226,46 @@ def gemm(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: boo
     d.c_stride[0], d.c_stride[1] = max(stc[0], 1), max(stc[1], 1)
     d.alpha, d.beta = alpha, beta
     d.epilogue = EPI_RELU if relu else EPI_NONE
+    d.max_ctas = int(max_ctas)
     _sync_torch_stream(A, B, C)
     _check(lib().accb_gemm(ctypes.byref(d), pa, pb, pc, pbias))
+
+
+def gemm_replicated(A, B, C_replicas, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: bool = False,
+                    compute: str = "tensor_2sm", max_ctas: int = 0) -> None:
+    """Tensor-core GEMM whose result is stored to every tensor of `C_replicas` (torch CUDA tensors with
+    identical shape and strides; replica 0 is the local C and is read when beta != 0, the others may be
+    peer / symmetric memory of other GPUs and are only written)."""
+    pa, ta, sha, sta, _ = _describe(A)
+    pb, tb, shb, stb, _ = _describe(B)
+    c0 = C_replicas[0]
+    pc, tc, shc, stc, _ = _describe(c0)
+    m, k = sha
+    k2, n = shb
+    if k2 != k or tuple(shc) != (m, n):
+        raise ValueError(f"shape mismatch: A{sha} B{shb} C{shc}")
+    ptrs = (ctypes.c_void_p * len(C_replicas))()
+    for i, c in enumerate(C_replicas):
+        if tuple(c.shape) != (m, n) or tuple(c.stride()) != tuple(c0.stride()) or c.dtype != c0.dtype:
+            raise ValueError("all C replicas must have the same shape, strides and dtype")
+        ptrs[i] = c.data_ptr()
+    pbias = None
+    if bias is not None:
+        pbias, tbias, shbias, _, _ = _describe(bias)
+        if tbias != F32 or tuple(shbias) != (n,):
+            raise ValueError("bias must be fp32 of length N")
+    d = GemmDesc()
+    d.m, d.n, d.k = m, n, k
+    d.a_type, d.b_type, d.c_type = ta, tb, tc
+    d.compute = _COMPUTE[compute]
+    d.a_stride[0], d.a_stride[1] = max(sta[0], 1), max(sta[1], 1)
+    d.b_stride[0], d.b_stride[1] = max(stb[0], 1), max(stb[1], 1)
+    d.c_stride[0], d.c_stride[1] = max(stc[0], 1), max(stc[1], 1)
+    d.alpha, d.beta = alpha, beta
+    d.epilogue = EPI_RELU if relu else EPI_NONE
+    d.max_ctas = int(max_ctas)
+    _sync_torch_stream(A, B, c0)
+    _check(lib().accb_gemm_replicated(ctypes.byref(d), pa, pb, ptrs, len(C_replicas), pbias))
 
 
 def reduce_mean_rank3_dims(d0: int, d1: int, d2: int, axes, keepdims: int = 1):

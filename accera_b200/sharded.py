@@ -14,8 +14,24 @@ tree); this is new work around the same HAT GEMM function.  One process per GPU:
   * The all-gather of chunk j runs on a second stream while the GEMM of chunk
     j+1 computes.
 
-No kernel reads or writes another GPU's memory; NCCL is the only cross-GPU mover.
-The data path has no other collective.
+Two ways to move the blocks, chosen with `gather=`:
+
+  "nccl"         one in-place ncclAllGather per chunk (the block-cyclic layout makes the `world`
+                 blocks of a chunk adjacent in C).  NCCL's kernels need SMs of their own; the
+                 tensor-core GEMM holds almost all shared memory of every SM it runs on, so the
+                 caller should leave a few SMs free (accb_gemm_desc.max_ctas).
+  "copy_engine"  C lives in symmetric memory (torch.distributed._symmetric_memory); as soon as a
+                 block is computed its owner pushes it into every peer's C with plain
+                 device-to-device copies, one stream per peer.  The DMA engines do the work over
+                 NVLink, no SM is taken from the GEMM, and one barrier at the end of the step
+                 tells every rank that all blocks have landed.
+
+  "fused"        C lives in symmetric memory and the GEMM kernel itself stores every output tile to
+                 all replicas of C (accb_gemm_replicated): TMA stores from the epilogue's shared-memory
+                 staging go to the local C and, over NVLink, to each peer's C, so the transfer overlaps
+                 the math tile by tile.  One barrier at the end of the step.
+
+The kernels never load from another GPU's memory and use no TMA multicast; "fused" only stores to it.
 """
 from __future__ import annotations
 
@@ -100,18 +116,49 @@ class ShardedGemm:
     """
 
     def __init__(self, plan: RowBlockPlan, rank: int, group=None, gemm_fn: Optional[Callable] = None,
-                 overlap: bool = True):
+                 overlap: bool = True, gather: str = "nccl", gemm_kwargs: Optional[dict] = None):
+        if gather not in ("nccl", "copy_engine", "fused"):
+            raise ValueError("gather must be 'nccl', 'copy_engine' or 'fused'")
+        self.gemm_kwargs = dict(gemm_kwargs) if gemm_kwargs is not None else dict(beta=0.0, relu=True, compute="tensor_2sm")
         self.plan = plan
         self.rank = rank
         self.group = group
         self.overlap = overlap
+        self.gather = gather
         self._gemm_fn = gemm_fn
         self._comm_stream = None
         self._events: List = []
+        self._symm = None          # symmetric-memory handle of C (copy_engine)
+        self._peer_c: List = []
+        self._peer_streams: List = []
+
+    @staticmethod
+    def allocate_c(m: int, n: int, dtype, device, group=None, gather: str = "nccl"):
+        """Allocates the full C for this rank: ordinary device memory for "nccl", symmetric memory (mapped
+        into every peer's address space) for "copy_engine"."""
+        import torch
+        if gather in ("copy_engine", "fused"):
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            c = symm_mem.empty((m, n), dtype=dtype, device=device)
+            c.zero_()
+            return c
+        return torch.zeros(m, n, dtype=dtype, device=device)
+
+    def _setup_copy_engine(self, c_full) -> None:
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        group = self.group if self.group is not None else dist.group.WORLD
+        self._symm = symm_mem.rendezvous(c_full, group)
+        if self._symm is None:
+            raise RuntimeError("copy_engine gather needs C allocated with ShardedGemm.allocate_c(..., gather='copy_engine')")
+        self._peer_c = [self._symm.get_buffer(r, tuple(c_full.shape), c_full.dtype) for r in range(self.plan.world)]
+        self._peer_streams = [torch.cuda.Stream(device=c_full.device) for _ in range(self.plan.world)]
 
     def _default_gemm(self, a, b, c):
         from . import runtime
-        runtime.gemm(a, b, c, beta=0.0, relu=True, compute="tensor_2sm")
+        runtime.gemm(a, b, c, **self.gemm_kwargs)
 
     def run(self, a_local, b, c_full) -> None:
         """a_local: this rank's rows ([rows_per_rank, K], from shard_rows); c_full: [M, N] on every rank."""
@@ -120,6 +167,10 @@ class ShardedGemm:
         plan = self.plan
         gemm = self._gemm_fn or self._default_gemm
         on_gpu = bool(getattr(c_full, "is_cuda", False))
+        if self.gather == "copy_engine" and plan.world > 1:
+            return self._run_copy_engine(a_local, b, c_full, gemm)
+        if self.gather == "fused" and plan.world > 1:
+            return self._run_fused(a_local, b, c_full)
         use_streams = on_gpu and self.overlap and plan.world > 1
         if use_streams and self._comm_stream is None:
             self._comm_stream = torch.cuda.Stream(device=c_full.device)
@@ -147,3 +198,44 @@ class ShardedGemm:
             w.wait()
         if use_streams:
             torch.cuda.current_stream(c_full.device).wait_stream(self._comm_stream)
+
+    def _run_copy_engine(self, a_local, b, c_full, gemm) -> None:
+        import torch
+        plan = self.plan
+        if self._symm is None:
+            self._setup_copy_engine(c_full)
+        main = torch.cuda.current_stream(c_full.device)
+        for j in range(plan.chunks):
+            l0, l1 = plan.local_row_range(j)
+            g0, g1 = plan.global_row_range(self.rank, j)
+            gemm(a_local[l0:l1], b, c_full[g0:g1])
+            done = torch.cuda.Event()
+            done.record(main)
+            src = c_full[g0:g1]
+            for step in range(1, plan.world):
+                peer = (self.rank + step) % plan.world          # every rank starts with a different peer
+                st = self._peer_streams[peer]
+                st.wait_event(done)
+                with torch.cuda.stream(st):
+                    self._peer_c[peer][g0:g1].copy_(src, non_blocking=True)
+        for step in range(1, plan.world):
+            main.wait_stream(self._peer_streams[(self.rank + step) % plan.world])
+        # all my pushes are ordered before the barrier on `main`; after it every peer's pushes have landed here
+        self._symm.barrier()
+
+    def _run_fused(self, a_local, b, c_full) -> None:
+        from . import runtime
+        plan = self.plan
+        if self._symm is None:
+            self._setup_copy_engine(c_full)
+        kw = {k: v for k, v in self.gemm_kwargs.items() if k in ("alpha", "beta", "relu", "compute", "max_ctas", "bias")}
+        for j in range(plan.chunks):
+            l0, l1 = plan.local_row_range(j)
+            g0, g1 = plan.global_row_range(self.rank, j)
+            # replica 0 is the local C (read when beta != 0); the others are the peers' C, each rank starting
+            # with a different peer so that the NVLink traffic of a step is spread over all destinations
+            replicas = [c_full[g0:g1]] + [self._peer_c[(self.rank + s) % plan.world][g0:g1] for s in range(1, plan.world)]
+            runtime.gemm_replicated(a_local[l0:l1], b, replicas, **kw)
+        # the stores of my launches are ordered before the barrier on this stream; after it all peers' tiles are here
+        self._symm.barrier()
+

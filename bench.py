@@ -284,22 +284,57 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if dist_on:
         dist.init_process_group("nccl", device_id=device)
     peaks = load_peaks()
-    plan = RowBlockPlan.choose(M, world, max_chunks=args.chunks)
+    plan = RowBlockPlan.choose(M, world, max_chunks=(1 if args.gather == "fused" and args.chunks_default else args.chunks))
     a_dev, b_dev = make_inputs(plan, rank, device)
-    c_full = torch.zeros(M, N, dtype=torch.bfloat16, device=device)
+    gather = args.gather if dist_on else "nccl"
+    c_full = ShardedGemm.allocate_c(M, N, torch.bfloat16, device, gather=gather)
     compute = args.compute
 
-    def gemm_fn(a, b, c):
-        # beta = 1: the HAT function is "C += A @ B, then ReLU" with C INPUT_OUTPUT; the step zeroes its C blocks first
-        rt.gemm(a, b, c, beta=1.0, relu=True, compute=compute)
+    # with several GPUs, leave a few SMs to the all-gather kernels of the previous chunk (they cannot share an
+    # SM with a GEMM CTA, which holds almost all of its shared memory)
+    max_ctas = 0
+    if dist_on and gather == "nccl" and args.comm_sms > 0:
+        max_ctas = max(2, torch.cuda.get_device_properties(device).multi_processor_count - args.comm_sms)
 
-    sg = ShardedGemm(plan, rank, gemm_fn=gemm_fn)
+    # beta = 1: the HAT function is "C += A @ B, then ReLU" with C INPUT_OUTPUT
+    gemm_kwargs = dict(beta=1.0, relu=True, compute=compute, max_ctas=max_ctas)
+
+    def gemm_fn(a, b, c):
+        rt.gemm(a, b, c, **gemm_kwargs)
+
+    sg = ShardedGemm(plan, rank, gemm_fn=gemm_fn, gather=gather, gemm_kwargs=gemm_kwargs)
 
     def step():
         # C starts as zeros and is INPUT_OUTPUT: every step reads it, adds A @ B, applies the ReLU and writes
         # it back (then all-gathers it).  It is not re-zeroed between steps: that is input preparation, not
         # the hot path, and the work per step does not depend on C's values.
         sg.run(a_dev, b_dev, c_full)
+
+    verified = None
+    if dist_on:
+        # one untimed step from C = 0, then check a block that ANOTHER rank computed and that reached this GPU
+        # through the gather, against torch's own matmul on a regenerated copy of that block's rows of A
+        step()
+        torch.cuda.synchronize(device)
+        other = (rank + 1) % world
+        j = plan.chunks - 1
+        g0, g1 = plan.global_row_range(other, j)
+        r = np.random.default_rng(2000 + plan.block_of(other, j))
+        rows = min(1024, plan.block_rows)
+        a_blk = torch.from_numpy(r.standard_normal((rows, K), dtype=np.float32)).to(device).to(torch.bfloat16)
+        want = torch.relu(a_blk.float() @ b_dev.float())
+        got = c_full[g0:g0 + rows].float()
+        err = (got - want).abs().max().item()
+        scale = want.abs().max().item()
+        ok = torch.tensor([1.0 if err <= 2e-2 * scale else 0.0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        verified = bool(ok.item() == 1.0)
+        if not verified:
+            raise SystemExit(f"rank {rank}: gathered block of rank {other} differs from the reference (max err {err}, scale {scale})")
+        c_full.zero_()
+        del a_blk, want, got
+        torch.cuda.synchronize(device)
+        dist.barrier()
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -383,7 +418,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "compute": compute,
                        "row_blocks": f"{plan.world * plan.chunks} blocks of {plan.block_rows} rows, block-cyclic",
-                       "chunks": plan.chunks, "l2": "inputs larger than L2 (A shard >= 128 MiB, B 128 MiB, C 1 GiB)",
+                       "chunks": plan.chunks, "gather": gather if dist_on else "none", "gemm_ctas": (max_ctas or "all SMs"), "l2": "inputs larger than L2 (A shard >= 128 MiB, B 128 MiB, C 1 GiB)",
                        "beta": 1.0, "peaks": peaks["source"]},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -396,6 +431,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                          "per": "GPU", "peak_source": peaks["source"] + " burst bf16 (cuBLAS)"},
             "cpu_baseline": cpu_baseline,
         }
+        if verified is not None:
+            line["gather_verified"] = verified
         if extras is not None:
             line["other_configs"] = extras
         print(json.dumps(line), flush=True)
@@ -412,8 +449,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--compute", default="tensor_2sm", choices=["tensor", "tensor_2sm"])
     ap.add_argument("--chunks", type=int, default=4, help="row-block rounds per rank for GEMM / all-gather overlap (N > 1)")
+    ap.add_argument("--gather", default="fused", choices=["nccl", "copy_engine", "fused"],
+                    help="how C is reassembled for N > 1: NCCL all-gather, DMA pushes into symmetric memory, or "
+                         "stores to every GPU's C from the GEMM epilogue itself")
+    ap.add_argument("--comm-sms", type=int, default=16, help="SMs the GEMM leaves to the concurrent all-gather (N > 1)")
     ap.add_argument("--no-extras", action="store_true", help="skip the device-timed numbers of the other configurations")
     args = ap.parse_args()
+    args.chunks_default = "--chunks" not in " ".join(sys.argv)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -86,11 +86,27 @@ typedef struct accb_gemm_desc {
     float alpha;
     float beta;
     int32_t epilogue;               /* ACCB_EPI_* */
-    int32_t reserved;
+    int32_t max_ctas;               /* tensor-core path: upper bound on the persistent grid (0 = one CTA per SM).
+                                       Leaving a few SMs free lets a collective running on another stream
+                                       make progress while the GEMM computes. */
 } accb_gemm_desc;
 
 /* bias may be NULL; when given it is n fp32 values added to every row before the ReLU */
 int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c, const float* bias);
+
+/*
+ * The same GEMM on the tensor cores, with the result stored to several replicas of C at once.
+ * (No counterpart in the reference, which has no multi-GPU path.)  c_replicas[0] is the local C: it is
+ * read when beta != 0 and written; c_replicas[1..n_replicas-1] receive the same values with the same
+ * layout and are only written.  They may be another GPU's memory mapped into this process (peer /
+ * symmetric memory): every output tile is then pushed over NVLink by TMA stores straight from the
+ * epilogue, so an M-row sharded GEMM reassembles C on all GPUs without a separate all-gather.
+ * Device pointers only; C must be row-major with a 16-byte aligned pitch and base; 1 <= n_replicas <= 8.
+ * The kernel's stores have completed when the launch has completed on its stream; making them visible
+ * to the other GPUs' later work (a barrier between the ranks) is the caller's job.
+ */
+int accb_gemm_replicated(const accb_gemm_desc* desc, const void* a, const void* b, void* const* c_replicas,
+                         int32_t n_replicas, const float* bias);
 
 /*
  * ReduceMean over a dense first-major rank-3 fp32 array.

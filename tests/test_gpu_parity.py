@@ -505,3 +505,55 @@ def test_simt_f32_cp_async_path_ragged(m, n, k, lda, ldb):
     got = C0.copy()
     rt.gemm(A, B, got, bias=bias, relu=True, compute="simt")
     _assert_close(got, want, _gemm_scale(A, B) + np.abs(C0) + np.abs(bias), RTOL_F32, f"simt cp.async {m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("kind,out_kind", [("bfloat16", "bfloat16"), ("float16", "float32"), ("int8", "int32")])
+@pytest.mark.parametrize("m,n,k", [(512, 768, 256), (300, 264, 200)])
+def test_gemm_replicated_writes_every_replica(kind, out_kind, m, n, k):
+    # the multi-destination epilogue, exercised on one GPU: three replicas of C in local memory
+    import torch
+    if kind == "int8":
+        k = (k + 15) // 16 * 16            # the tensor path needs a 16-byte row pitch
+    dev = torch.device("cuda:0")
+    tmap = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32, "int8": torch.int8, "int32": torch.int32}
+    g = torch.Generator(device="cpu").manual_seed(m + n)
+    if kind == "int8":
+        A = torch.randint(-128, 128, (m, k), generator=g, dtype=torch.int8).to(dev)
+        Bt = torch.randint(-128, 128, (n, k), generator=g, dtype=torch.int8).to(dev)
+        C0 = torch.randint(-1000, 1000, (m, n), generator=g, dtype=torch.int32).to(dev)
+    else:
+        A = torch.randn(m, k, generator=g).to(dev).to(tmap[kind])
+        Bt = (torch.randn(n, k, generator=g) / k ** 0.5).to(dev).to(tmap[kind])
+        C0 = torch.randn(m, n, generator=g).to(dev).to(tmap[out_kind])
+    B = Bt.t()
+    want = C0.clone()
+    rt.gemm(A, B, want, beta=1.0, relu=True, compute="tensor_2sm")
+    reps = [C0.clone(), torch.zeros_like(C0), torch.full_like(C0, 3)]
+    rt.gemm_replicated(A, B, reps, beta=1.0, relu=True)
+    rt.synchronize()
+    for r in reps:
+        assert torch.equal(r, want)
+    # and against the oracle
+    a_np, b_np = A.cpu().view(torch.int16 if kind == "bfloat16" else A.dtype).numpy(), Bt.cpu().view(torch.int16 if kind == "bfloat16" else Bt.dtype).numpy().T
+    if kind == "bfloat16":
+        a_np, b_np = a_np.view(np.uint16), b_np.view(np.uint16)
+    c_np = C0.cpu().view(torch.int16 if out_kind == "bfloat16" else C0.dtype).numpy().copy()
+    if out_kind == "bfloat16":
+        c_np = c_np.view(np.uint16)
+    want_o = oracle.gemm(a_np, b_np, c_np, in_kind=kind, out_kind=out_kind, relu=True)
+    got_np = reps[1].cpu().view(torch.int16 if out_kind == "bfloat16" else C0.dtype).numpy()
+    if kind == "int8":
+        assert np.array_equal(got_np, want_o)
+    else:
+        gf = oracle.bf16_bits_to_f32(got_np.view(np.uint16)) if out_kind == "bfloat16" else got_np
+        wf = oracle.bf16_bits_to_f32(want_o) if out_kind == "bfloat16" else want_o
+        assert np.abs(gf - wf).max() <= 2e-2 * max(1.0, np.abs(wf).max())
+
+
+def test_direct_store_epilogue_still_matches(monkeypatch):
+    # the epilogue without shared-memory staging (used for column-major or unaligned C), forced on an aligned C
+    monkeypatch.setenv("ACCB_GEMM_TUNE", "t=0")
+    _tensor_case("bfloat16", "bfloat16", 384, 520, 320, "tensor_2sm", beta=1.0, use_bias=True)
+    _tensor_case("float16", "float32", 200, 300, 136, "tensor", beta=1.0)
+    monkeypatch.delenv("ACCB_GEMM_TUNE")
+    _tensor_case("bfloat16", "bfloat16", 384, 520, 320, "tensor_2sm", beta=1.0, use_bias=True)
