@@ -67,8 +67,8 @@ template <bool TWO_SM> struct SmemPlan {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = TWO_SM ? 6 : 4;
     static constexpr int kBarrierBytes = 256;
-    // epilogue staging for TMA stores: per epilogue warp two boxes of 32 rows x 32 elements (<= 4 bytes each)
-    static constexpr int kStoreBoxBytes = 32 * 32 * 4;
+    // epilogue staging for TMA stores: per epilogue warp two boxes of 32 rows x 128 bytes (128-byte swizzle)
+    static constexpr int kStoreBoxBytes = 32 * 128;
     static constexpr int kStoreBytes = kEpiWarps * 2 * kStoreBoxBytes;
     static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + kStoreBytes + 1024;   // +1024: manual alignment
 };
@@ -392,8 +392,11 @@ __device__ __forceinline__ void epilogue_row(const uint32_t (&acc)[32], TC* __re
 template <typename TC, typename ACC>
 __device__ __forceinline__ void epilogue_to_smem(const uint32_t (&acc)[32], const TC* __restrict__ crow, bool row_ok,
                                                  int64_t col0, int ncols, bool c_vec, const float* __restrict__ bias,
-                                                 const UmmaParams& p, TC* srow)
+                                                 const UmmaParams& p, uint8_t* srow, int slot0, int lane7)
 {
+    // srow: this thread's 128-byte row of the staging box; the 32 results occupy 16-byte slots
+    // slot0 .. slot0 + (32 * sizeof(TC) / 16) - 1, each stored at slot ^ (row % 8): the 128-byte swizzle of
+    // the TMA store map, which also makes the 8 rows of a store phase hit 8 different bank groups
     const bool full = (ncols == 32);
     if constexpr (std::is_same<ACC, int>::value) {
         int v[32];
@@ -416,9 +419,9 @@ __device__ __forceinline__ void epilogue_to_smem(const uint32_t (&acc)[32], cons
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = max(v[j], 0);
         }
-        int4* dst = reinterpret_cast<int4*>(srow);
 #pragma unroll
-        for (int q = 0; q < 8; ++q) dst[q] = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<int4*>(srow + (((slot0 + q) ^ lane7) << 4)) = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
     } else {
         float v[32];
 #pragma unroll
@@ -466,18 +469,17 @@ __device__ __forceinline__ void epilogue_to_smem(const uint32_t (&acc)[32], cons
             for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
         }
         if constexpr (sizeof(TC) == 4) {
-            float4* dst = reinterpret_cast<float4*>(srow);
 #pragma unroll
-            for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(srow + (((slot0 + q) ^ lane7) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         } else {
-            uint4* dst = reinterpret_cast<uint4*>(srow);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint4 o;
                 TC* h = reinterpret_cast<TC*>(&o);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) h[e] = (TC)v[8 * q + e];
-                dst[q] = o;
+                *reinterpret_cast<uint4*>(srow + (((slot0 + q) ^ lane7) << 4)) = o;
             }
         }
     }
@@ -498,12 +500,12 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // 1024-byte alignment: required by the 128B swizzle pattern shared by TMA and the MMA descriptors
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t bars = smem_base + S * Plan::kStageBytes;
+    const uint32_t bars = smem_base + S * Plan::kStageBytes + Plan::kStoreBytes;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
     auto tmem_full_bar = [&](int b) { return bars + 8u * (2 * S + b); };
     auto tmem_empty_bar = [&](int b) { return bars + 8u * (2 * S + 2 + b); };
-    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_gen + S * Plan::kStageBytes + 8 * (2 * S + 4));
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_gen + S * Plan::kStageBytes + Plan::kStoreBytes + 8 * (2 * S + 4));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -614,8 +616,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int local = 0;
         bool ok = true;
         uint32_t store_count = 0;                    // TMA-store boxes this warp has issued (warp-uniform)
-        uint8_t* store_stage = smem_gen + S * Plan::kStageBytes + Plan::kBarrierBytes +
-                               (size_t)(warp - 2) * 2 * Plan::kStoreBoxBytes;
+        uint8_t* store_stage = smem_gen + S * Plan::kStageBytes + (size_t)(warp - 2) * 2 * Plan::kStoreBoxBytes;
         for (int t = unit; t < num_tiles && ok; t += num_units, ++local) {
             int tm, tn;
             tile_coords(t, p, tm, tn);
@@ -640,25 +641,33 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         const int ncols = (int)min((int64_t)32, p.n - col0);
                         epilogue_row<TC, ACC>(acc, crow, col0, ncols, c_vec, p.cs1, bias, p);
                     }
-                } else if (row0 < p.m && col0 < p.n) {        // warp-uniform: the box has something to store
-                    const int ncols = (int)min((int64_t)32, p.n - col0);
-                    const int sb = (int)(store_count & 1u);
-                    // the box about to be overwritten was handed to TMA two chunks ago: wait until it has been read
-                    if (store_count >= 2) {
+                } else {
+                    // a staging box is 128 bytes wide: one 32-column chunk of 4-byte results, two of 2-byte ones
+                    constexpr int CPB = (sizeof(TC) == 4) ? 1 : 2;
+                    const int sub = c % CPB;
+                    const int64_t box_col0 = col0 - (int64_t)sub * 32;
+                    const bool box_live = (row0 < p.m) && (box_col0 < p.n);      // warp-uniform
+                    uint8_t* box = store_stage + (size_t)(store_count & 1u) * Plan::kStoreBoxBytes;
+                    if (box_live && sub == 0 && store_count >= 2) {
+                        // the box about to be overwritten was handed to TMA two boxes ago: wait until it has been read
                         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                         __syncwarp();
                     }
-                    uint8_t* box = store_stage + (size_t)sb * Plan::kStoreBoxBytes;
-                    epilogue_to_smem<TC, ACC>(acc, crow, row < p.m, col0, ncols, c_vec, bias, p,
-                                              reinterpret_cast<TC*>(box) + lane * 32);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to TMA
-                    __syncwarp();
-                    if (lane == 0) {
-                        const uint32_t src = smem_u32(box);
-                        for (int r = 0; r < p.n_replicas; ++r) tma_store_2d(&cmaps.m[r], src, (int)col0, (int)row0);
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    if (box_live && col0 < p.n) {
+                        const int ncols = (int)min((int64_t)32, p.n - col0);
+                        epilogue_to_smem<TC, ACC>(acc, crow, row < p.m, col0, ncols, c_vec, bias, p, box + lane * 128,
+                                                  sub * (32 * (int)sizeof(TC) / 16), lane & 7);
                     }
-                    ++store_count;
+                    if (box_live && sub == CPB - 1) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to TMA
+                        __syncwarp();
+                        if (lane == 0) {
+                            const uint32_t src = smem_u32(box);
+                            for (int r = 0; r < p.n_replicas; ++r) tma_store_2d(&cmaps.m[r], src, (int)box_col0, (int)row0);
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                        ++store_count;
+                    }
                 }
             }
             // this warp has drained its part of the accumulator: hand it back to the MMA issuer
@@ -742,7 +751,7 @@ bool make_operand_map(CUtensorMap* map, const void* base, int type, int64_t rows
     return r == CUDA_SUCCESS;
 }
 
-// C (or a replica of it) as a row-major [m, n] tensor; box = 32 x 32 elements, no swizzle
+// C (or a replica of it) as a row-major [m, n] tensor; box = 32 rows of 128 bytes, 128-byte swizzle
 bool make_c_map(CUtensorMap* map, void* base, int type, int64_t m, int64_t n, int64_t ld)
 {
     EncodeTiledFn enc = encode_tiled_fn();
@@ -757,10 +766,10 @@ bool make_c_map(CUtensorMap* map, void* base, int type, int64_t m, int64_t n, in
     const int es = elem_size(type);
     cuuint64_t dims[2] = { (cuuint64_t)n, (cuuint64_t)m };
     cuuint64_t strides[1] = { (cuuint64_t)(ld * es) };
-    cuuint32_t box[2] = { 32, 32 };
+    cuuint32_t box[2] = { (cuuint32_t)(128 / es), 32 };
     cuuint32_t estr[2] = { 1, 1 };
     CUresult r = enc(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
