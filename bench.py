@@ -37,6 +37,12 @@ UNIT = "TFLOP/s"
 WORKLOAD = "sharded bf16 GEMM+ReLU M=65536 N=8192 K=8192 (A row-major by M-row blocks, B col-major replicated, bf16 C all-gathered)"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel on this workload, from an
+# ncu capture of `python -m accera_b200.profile_cases gemm_bf16 --m 65536` (profiles/gemm_umma_bf16_65536x8192x8192.md).
+# Only the single-GPU launch (M = 65536) was captured; other shard sizes report null.
+NCU_TRAFFIC_BYTES = {("tensor_2sm", 1): 22.76e9}
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -427,7 +433,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "roofline": {"bound": "tensor", "achieved": kernel_tflops,
                          "peak": peak, "unit": "TFLOP/s", "frac": kernel_tflops / peak,
                          "frac_of_sustained_peak": (kernel_tflops / peaks["bf16_tflops_sustained"]) if peaks.get("bf16_tflops_sustained") else None,
-                         "traffic": None, "kernel": "gemm_umma_kernel<bf16,cta_group::2>" if compute == "tensor_2sm" else "gemm_umma_kernel<bf16>",
+                         "traffic": NCU_TRAFFIC_BYTES.get((compute, world)), "kernel": "gemm_umma_kernel<bf16,cta_group::2>" if compute == "tensor_2sm" else "gemm_umma_kernel<bf16>",
                          "per": "GPU", "peak_source": peaks["source"] + " burst bf16 (cuBLAS)"},
             "cpu_baseline": cpu_baseline,
         }
