@@ -87,9 +87,9 @@ int device_state(DeviceState** out, int* dev_out)
             return fail(ACCB_ERR_CUDA, buf);
         }
         s.num_sms = prop.multiProcessorCount;
-        e = cudaMalloc(&s.status, kStatusWords * sizeof(int));
+        e = cudaMalloc(&s.status, (kStatusWords + kPaceSlots) * sizeof(int));
         if (e != cudaSuccess) return fail_cuda("cudaMalloc(status)", e);
-        e = cudaMemset(s.status, 0, kStatusWords * sizeof(int));
+        e = cudaMemset(s.status, 0, (kStatusWords + kPaceSlots) * sizeof(int));
         if (e != cudaSuccess) return fail_cuda("cudaMemset(status)", e);
         e = cudaMallocHost(&s.status_host, kStatusWords * sizeof(int));
         if (e != cudaSuccess) return fail_cuda("cudaMallocHost(status)", e);

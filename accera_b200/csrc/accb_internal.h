@@ -18,6 +18,9 @@ namespace accb {
 //   [2] tcgen05 GEMM: k-block / tile the wait was at
 //   [3] reserved
 constexpr int kStatusWords = 4;
+// The status buffer is followed by kPaceSlots counters: one per in-flight tensor-core GEMM launch,
+// used to keep its persistent CTAs roughly in step (see gemm_umma.cu).
+constexpr int kPaceSlots = 64;
 
 struct GemmLaunch {
     accb_gemm_desc d;

@@ -40,7 +40,7 @@ WORKLOAD = "sharded bf16 GEMM+ReLU M=65536 N=8192 K=8192 (A row-major by M-row b
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel on this workload, from an
 # ncu capture of `python -m accera_b200.profile_cases gemm_bf16 --m 65536` (profiles/gemm_umma_bf16_65536x8192x8192.md).
 # Only the single-GPU launch (M = 65536) was captured; other shard sizes report null.
-NCU_TRAFFIC_BYTES = {("tensor_2sm", 1): 22.76e9}
+NCU_TRAFFIC_BYTES = {("tensor_2sm", 1): 12.74e9}
 
 
 def load_peaks():
