@@ -390,15 +390,7 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err)
     if (a == ACCB_F32 && b == ACCB_F32 && c == ACCB_F32) {
         if (f32_rr_ok(g, p)) {
             const int64_t tiles64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
-            int variant = -1;
-            if (const char* v = getenv("ACCB_SIMT_VARIANT")) variant = atoi(v);     // experiments only
-            if (variant == 0) e = launch_f32_rr<32, 64, 32, 2, 4, 4>(g, p);
-            else if (variant == 1) e = launch_f32_rr<32, 64, 32, 4, 4, 4>(g, p);
-            else if (variant == 2) e = launch_f32_rr<32, 32, 32, 2, 4, 4>(g, p);
-            else if (variant == 3) e = launch_f32_rr<64, 64, 32, 4, 4, 3>(g, p);
-            else if (variant == 4) e = launch_f32_rr<16, 64, 32, 2, 4, 4>(g, p);
-            else if (variant == 5) e = launch_f32_rr<32, 64, 16, 2, 4, 6>(g, p);
-            else if (tiles64 >= 2 * (int64_t)g.num_sms) e = launch_f32_rr<64, 64, 32, 4, 4, 3>(g, p);
+            if (tiles64 >= 2 * (int64_t)g.num_sms) e = launch_f32_rr<64, 64, 32, 4, 4, 3>(g, p);
             else e = launch_f32_rr<32, 64, 32, 2, 4, 4>(g, p);       // small problems: more, smaller tiles
         } else {
             e = launch_typed<float, float, float, float>(g, p);

@@ -90,6 +90,7 @@ struct UmmaParams {
     int c_stream;           // read / write C with streaming (evict-first) accesses
     int tma_store;          // epilogue goes through shared memory and TMA stores (row-major C with 16-byte pitch)
     int n_replicas;         // number of C replicas the result is stored to (1 = just C); replicas may be peer memory
+    int a_mn, b_mn;         // operand is MN-contiguous in global memory (column-major A / row-major B)
     int pace_pct;           // 0 = off; else a CTA starts loading its i-th tile only once pace_pct % of all CTAs'
                             // (i-1)-th tiles have been loaded (or a few microseconds have passed)
     int* pace;              // this launch's progress counter
@@ -188,6 +189,20 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr)
     d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
     d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
     d |= (uint64_t)2 << 61;                            // layout: 128-byte swizzle
+    return d;
+}
+
+// MN-major operand tile as TMA writes it from an MN-contiguous array: boxes of [k rows][128 bytes of MN] with
+// the 128-byte swizzle; 8 k-rows form one 1024-byte swizzle atom (stride byte offset), consecutive 128-byte
+// MN blocks are `mn_block_bytes` apart (leading byte offset).
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32_t mn_block_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)((mn_block_bytes >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
     return d;
 }
 
@@ -581,12 +596,27 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint32_t sb = sa + Plan::kABytes;
                     if constexpr (TWO_SM) {
                         if (leader) mbar_arrive_expect_tx(full_bar(s), 2u * Plan::kStageBytes);
-                        tma_load_2d_pair(sa, &map_a, full_bar(s), kb * slab_elems, row_a, pol_a);
-                        tma_load_2d_pair(sb, &map_b, full_bar(s), kb * slab_elems, row_b, pol_b);
                     } else {
                         mbar_arrive_expect_tx(full_bar(s), (uint32_t)Plan::kStageBytes);
-                        tma_load_2d(sa, &map_a, full_bar(s), kb * slab_elems, row_a, pol_a);
-                        tma_load_2d(sb, &map_b, full_bar(s), kb * slab_elems, row_b, pol_b);
+                    }
+                    auto load = [&](uint32_t dst, const CUtensorMap* map, int c0, int c1, uint64_t pol) {
+                        if constexpr (TWO_SM) tma_load_2d_pair(dst, map, full_bar(s), c0, c1, pol);
+                        else tma_load_2d(dst, map, full_bar(s), c0, c1, pol);
+                    };
+                    // K-major operand: one box [rows][128 B of K].  MN-major operand: one box [k rows][128 B of MN]
+                    // per 128-byte block of the tile's MN extent, stacked in shared memory.
+                    if (!p.a_mn) {
+                        load(sa, &map_a, kb * slab_elems, row_a, pol_a);
+                    } else {
+                        for (int blk = 0; blk < kBlockM / slab_elems; ++blk)
+                            load(sa + blk * (kSlabBytes * slab_elems), &map_a, row_a + blk * slab_elems, kb * slab_elems, pol_a);
+                    }
+                    constexpr int kRowsB = TWO_SM ? kBlockN / 2 : kBlockN;
+                    if (!p.b_mn) {
+                        load(sb, &map_b, kb * slab_elems, row_b, pol_b);
+                    } else {
+                        for (int blk = 0; blk < kRowsB / slab_elems; ++blk)
+                            load(sb + blk * (kSlabBytes * slab_elems), &map_b, row_b + blk * slab_elems, kb * slab_elems, pol_b);
                     }
                 }
                 if (p.pace_pct > 0 && leader && ok) atomicAdd(p.pace, 1);   // counted even after this CTA stopped waiting
@@ -611,13 +641,17 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t sa = smem_base + s * Plan::kStageBytes;
                     const uint32_t sb = sa + Plan::kABytes;
-                    const uint64_t adesc = make_smem_desc(sa);
-                    const uint64_t bdesc = make_smem_desc(sb);
+                    // K-major: advancing K inside the swizzle atom is +32 bytes on the start address.
+                    // MN-major: one MMA consumes (32 / elem_bytes) k-rows of 128 bytes each.
+                    const uint32_t mn_block = (uint32_t)(kSlabBytes * slab_elems);
+                    const uint32_t mn_step = (uint32_t)((kMmaKBytes / p.elem_bytes) * kSlabBytes);
+                    const uint64_t adesc = p.a_mn ? make_smem_desc_mn(sa, mn_block) : make_smem_desc(sa);
+                    const uint64_t bdesc = p.b_mn ? make_smem_desc_mn(sb, mn_block) : make_smem_desc(sb);
+                    const uint64_t astep = (uint64_t)((p.a_mn ? mn_step : (uint32_t)kMmaKBytes) >> 4);
+                    const uint64_t bstep = (uint64_t)((p.b_mn ? mn_step : (uint32_t)kMmaKBytes) >> 4);
 #pragma unroll
                     for (int j = 0; j < kSlabBytes / kMmaKBytes; ++j) {
-                        // advancing K inside the swizzle atom: +32 bytes on the start address (16-byte units)
-                        umma<KIND, TWO_SM>(tmem_d, adesc + (uint64_t)(j * (kMmaKBytes >> 4)),
-                                           bdesc + (uint64_t)(j * (kMmaKBytes >> 4)), p.idesc,
+                        umma<KIND, TWO_SM>(tmem_d, adesc + (uint64_t)j * astep, bdesc + (uint64_t)j * bstep, p.idesc,
                                            (kb > 0 || j > 0) ? 1u : 0u);
                     }
                     umma_commit<TWO_SM>(empty_bar(s));            // frees the stage once these MMAs have read it
@@ -747,7 +781,8 @@ int elem_size(int t)
 }
 
 // K-major operand [rows, k] with `ld` elements between rows; box = 128 bytes of K by box_rows rows
-bool make_operand_map(CUtensorMap* map, const void* base, int type, int64_t rows, int64_t k, int64_t ld, int box_rows)
+bool make_operand_map(CUtensorMap* map, const void* base, int type, int64_t rows, int64_t k, int64_t ld, int box_rows,
+                      bool mn_major = false)
 {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return false;
@@ -759,9 +794,11 @@ bool make_operand_map(CUtensorMap* map, const void* base, int type, int64_t rows
     default: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
     }
     const int es = elem_size(type);
-    cuuint64_t dims[2] = { (cuuint64_t)k, (cuuint64_t)rows };
+    // K-major: [rows][k], k contiguous, box = 128 bytes of k by box_rows rows.
+    // MN-major: the array is [k][rows] with `rows` (M or N) contiguous; box = 128 bytes of M/N by (128 / es) k-rows.
+    cuuint64_t dims[2] = { (cuuint64_t)(mn_major ? rows : k), (cuuint64_t)(mn_major ? k : rows) };
     cuuint64_t strides[1] = { (cuuint64_t)(ld * es) };
-    cuuint32_t box[2] = { (cuuint32_t)(kSlabBytes / es), (cuuint32_t)box_rows };
+    cuuint32_t box[2] = { (cuuint32_t)(kSlabBytes / es), (cuuint32_t)(mn_major ? kSlabBytes / es : box_rows) };
     cuuint32_t estr[2] = { 1, 1 };
     CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -796,7 +833,7 @@ bool c_tma_storable(const accb_gemm_desc& d, const void* c)
            (reinterpret_cast<uintptr_t>(c) & 15) == 0;
 }
 
-uint32_t make_idesc(int a_type, int b_type, bool int_acc, bool f16_out_acc, int m, int n)
+uint32_t make_idesc(int a_type, int b_type, bool int_acc, bool f16_out_acc, int m, int n, bool a_mn = false, bool b_mn = false)
 {
     auto fmt = [](int t) -> uint32_t {
         switch (t) {
@@ -808,7 +845,9 @@ uint32_t make_idesc(int a_type, int b_type, bool int_acc, bool f16_out_acc, int 
     d |= (int_acc ? 2u : (f16_out_acc ? 0u : 1u)) << 4;   // accumulator format: s32 / f16 / f32
     d |= fmt(a_type) << 7;
     d |= fmt(b_type) << 10;
-    // bits 13, 14: no negation; bits 15, 16: both operands K-major
+    // bits 13, 14: no negation; bits 15, 16: operand major-ness (0 = K-major, 1 = MN-major)
+    d |= (a_mn ? 1u : 0u) << 15;
+    d |= (b_mn ? 1u : 0u) << 16;
     d |= (uint32_t)(n >> 3) << 17;
     d |= (uint32_t)(m >> 4) << 24;
     return d;
@@ -863,9 +902,17 @@ bool gemm_umma_supported(const GemmLaunch& g, const char** why)
     const bool i8 = ((a == ACCB_S8 || a == ACCB_U8) && (b == ACCB_S8 || b == ACCB_U8) && c == ACCB_S32);
     if (!(f16_family || tf32 || i8)) { *why = "element types have no tensor-core path"; return false; }
     if (i8 && (d.alpha != 1.0f || (d.beta != 0.0f && d.beta != 1.0f) || g.bias)) { *why = "integer GEMM supports alpha=1, beta in {0,1}, no bias"; return false; }
-    if (d.a_stride[1] != 1 || d.b_stride[0] != 1) { *why = "tensor-core path needs K-contiguous A (row-major) and B (column-major)"; return false; }
+    // each operand must be contiguous along K (row-major A / column-major B) or along M / N (column-major A /
+    // row-major B); the other stride is the pitch
+    const bool a_k = d.a_stride[1] == 1, a_mn = !a_k && d.a_stride[0] == 1;
+    const bool b_k = d.b_stride[0] == 1, b_mn = !b_k && d.b_stride[1] == 1;
+    if (!(a_k || a_mn) || !(b_k || b_mn)) { *why = "tensor-core path needs unit stride along one dimension of A and of B"; return false; }
+    // 32-bit (TF32) operands are taken K-contiguous only: their M / N-contiguous form needs a different
+    // shared-memory swizzle (32-byte base atom) that this kernel does not stage
+    if (tf32 && (a_mn || b_mn)) { *why = "TF32 tensor path needs K-contiguous A (row-major) and B (column-major)"; return false; }
     const int es = elem_size(a);
-    if ((d.a_stride[0] * es) % 16 || (d.b_stride[1] * es) % 16) { *why = "operand row pitch must be a multiple of 16 bytes"; return false; }
+    const int64_t pitch_a = a_k ? d.a_stride[0] : d.a_stride[1], pitch_b = b_k ? d.b_stride[1] : d.b_stride[0];
+    if ((pitch_a * es) % 16 || (pitch_b * es) % 16) { *why = "operand row pitch must be a multiple of 16 bytes"; return false; }
     if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15)) { *why = "operand base must be 16-byte aligned"; return false; }
     if (d.m < 1 || d.n < 1 || d.k < 1) { *why = "empty problem"; return false; }
     if (d.m > (int64_t)1 << 30 || d.n > (int64_t)1 << 30 || d.k > (int64_t)1 << 30) { *why = "dimension too large"; return false; }
@@ -881,8 +928,9 @@ int launch_gemm_umma(const GemmLaunch& g, bool two_sm, const char** err)
 
     CUtensorMap ma, mb;
     const int b_box_rows = two_sm ? kBlockN / 2 : kBlockN;
-    if (!make_operand_map(&ma, g.a, d.a_type, d.m, d.k, d.a_stride[0], kBlockM) ||
-        !make_operand_map(&mb, g.b, d.b_type, d.n, d.k, d.b_stride[1], b_box_rows)) {
+    const bool a_mn = d.a_stride[1] != 1, b_mn = d.b_stride[0] != 1;
+    if (!make_operand_map(&ma, g.a, d.a_type, d.m, d.k, a_mn ? d.a_stride[1] : d.a_stride[0], kBlockM, a_mn) ||
+        !make_operand_map(&mb, g.b, d.b_type, d.n, d.k, b_mn ? d.b_stride[0] : d.b_stride[1], b_box_rows, b_mn)) {
         *err = "tcgen05 GEMM: cuTensorMapEncodeTiled failed";
         return ACCB_ERR_CUDA;
     }
@@ -892,7 +940,8 @@ int launch_gemm_umma(const GemmLaunch& g, bool two_sm, const char** err)
     p.m = d.m; p.n = d.n; p.k = d.k;
     p.cs0 = d.c_stride[0]; p.cs1 = d.c_stride[1];
     p.alpha = d.alpha; p.beta = d.beta; p.relu = (d.epilogue == ACCB_EPI_RELU);
-    p.idesc = make_idesc(d.a_type, d.b_type, int_acc, false, two_sm ? 2 * kBlockM : kBlockM, kBlockN);
+    p.idesc = make_idesc(d.a_type, d.b_type, int_acc, false, two_sm ? 2 * kBlockM : kBlockM, kBlockN, a_mn, b_mn);
+    p.a_mn = a_mn; p.b_mn = b_mn;
     p.elem_bytes = elem_size(d.a_type);
     const int rows_per_unit = two_sm ? 2 * kBlockM : kBlockM;
     p.tiles_m = (int)((d.m + rows_per_unit - 1) / rows_per_unit);

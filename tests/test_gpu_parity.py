@@ -131,12 +131,17 @@ def test_simt_narrow_inputs(kind):
 # tensor-core (tcgen05) GEMM
 # ---------------------------------------------------------------------------
 
-def _tensor_case(kind, out_kind, m, n, k, compute, *, beta=0.0, relu=True, use_bias=False, alpha=1.0, seed=0):
+def _tensor_case(kind, out_kind, m, n, k, compute, *, beta=0.0, relu=True, use_bias=False, alpha=1.0, seed=0,
+                 a_order="C", b_order="F"):
+    """a_order "C" = row-major A (K-contiguous), "F" = column-major A (M-contiguous);
+    b_order "F" = column-major B (K-contiguous), "C" = row-major B (N-contiguous)."""
     rng = np.random.default_rng(seed + m * 7 + n * 3 + k)
+    _a = (lambda x: np.asfortranarray(x)) if a_order == "F" else (lambda x: np.ascontiguousarray(x))
+    _b = (lambda x: np.asfortranarray(x)) if b_order == "F" else (lambda x: np.ascontiguousarray(x))
     if kind in ("int8", "uint8"):
         lo, hi = (-128, 128) if kind == "int8" else (0, 256)
-        A = rng.integers(lo, hi, size=(m, k)).astype(kind)
-        B = np.asfortranarray(rng.integers(lo, hi, size=(k, n)).astype(kind))
+        A = _a(rng.integers(lo, hi, size=(m, k)).astype(kind))
+        B = _b(rng.integers(lo, hi, size=(k, n)).astype(kind))
         C0 = rng.integers(-1000, 1000, size=(m, n)).astype(np.int32) if beta else np.zeros((m, n), np.int32)
         want = oracle.gemm(A, B, C0.copy(), beta=beta, relu=relu)
         got = C0.copy()
@@ -150,14 +155,14 @@ def _tensor_case(kind, out_kind, m, n, k, compute, *, beta=0.0, relu=True, use_b
     Bf = rng.standard_normal((k, n), dtype=np.float32) / np.float32(np.sqrt(k))
     kw = {}
     if kind == "float16":
-        A, B = Af.astype(np.float16), np.asfortranarray(Bf.astype(np.float16))
+        A, B = _a(Af.astype(np.float16)), _b(Bf.astype(np.float16))
         A64, B64 = A.astype(np.float64), B.astype(np.float64)
     elif kind == "bfloat16":
-        A, B = oracle.f32_to_bf16_bits(Af), np.asfortranarray(oracle.f32_to_bf16_bits(Bf))
+        A, B = _a(oracle.f32_to_bf16_bits(Af)), _b(oracle.f32_to_bf16_bits(Bf))
         A64, B64 = oracle.bf16_bits_to_f32(A).astype(np.float64), oracle.bf16_bits_to_f32(B).astype(np.float64)
         kw["kind"] = "bfloat16"
     else:   # float32 computed as TF32
-        A, B = Af, np.asfortranarray(Bf)
+        A, B = _a(Af), _b(Bf)
         A64, B64 = A.astype(np.float64), B.astype(np.float64)
     C0f = rng.standard_normal((m, n), dtype=np.float32) if beta else np.zeros((m, n), np.float32)
     if out_kind == "float32":
@@ -219,11 +224,12 @@ def test_tensor_persistent_many_tiles():
     _tensor_case("bfloat16", "bfloat16", 4096, 4096, 256, "tensor_2sm", beta=1.0)
 
 
-def test_auto_dispatch_falls_back_to_simt_for_row_major_b():
-    # B row-major is not K-contiguous: AUTO must still give the right answer (SIMT kernel)
+def test_auto_dispatch_falls_back_to_simt_for_unaligned_pitch():
+    # a row pitch that is not a multiple of 16 bytes cannot be described to TMA: AUTO must still give the
+    # right answer (SIMT kernel), an explicit tensor request must fail loudly
     rng = np.random.default_rng(5)
-    A = rng.standard_normal((64, 128), dtype=np.float32).astype(np.float16)
-    B = rng.standard_normal((128, 96), dtype=np.float32).astype(np.float16)
+    A = rng.standard_normal((64, 100), dtype=np.float32).astype(np.float16)        # pitch 200 bytes
+    B = np.asfortranarray(rng.standard_normal((100, 96), dtype=np.float32).astype(np.float16))
     C = np.zeros((64, 96), np.float32)
     want = oracle.gemm(A, B, C.copy(), relu=True)
     rt.gemm(A, B, C, relu=True)
@@ -557,3 +563,41 @@ def test_direct_store_epilogue_still_matches(monkeypatch):
     _tensor_case("float16", "float32", 200, 300, 136, "tensor", beta=1.0)
     monkeypatch.delenv("ACCB_GEMM_TUNE")
     _tensor_case("bfloat16", "bfloat16", 384, 520, 320, "tensor_2sm", beta=1.0, use_bias=True)
+
+
+def test_tensor_gemm_random_shapes_fuzz():
+    # seeded sweep over ragged shapes, all element types, both CTA modes, beta / bias / relu on and off;
+    # every K whose row pitch is 16-byte aligned is legal, including K shorter than one 128-byte slab
+    rng = np.random.default_rng(20251)
+    kinds = [("bfloat16", "float32", 8), ("bfloat16", "bfloat16", 8), ("float16", "float16", 8), ("float16", "float32", 8),
+             ("float32", "float32", 4), ("int8", "int32", 16), ("uint8", "int32", 16)]
+    for it in range(48):
+        kind, out_kind, kq = kinds[it % len(kinds)]
+        m = int(rng.integers(1, 700))
+        n = int(rng.integers(1, 900))
+        k = int(rng.integers(1, 40)) * kq
+        compute = "tensor" if it % 2 else "tensor_2sm"
+        beta = float(rng.integers(0, 2))
+        _tensor_case(kind, out_kind, m, n, k, compute, beta=beta, relu=bool(rng.integers(0, 2)),
+                     use_bias=bool(rng.integers(0, 2)) and kind not in ("int8", "uint8"), seed=it)
+
+
+@pytest.mark.parametrize("compute", TENSOR_MODES)
+@pytest.mark.parametrize("a_order,b_order", [("F", "F"), ("C", "C"), ("F", "C")])
+@pytest.mark.parametrize("kind,out_kind", [("bfloat16", "float32"), ("float16", "float16"), ("uint8", "int32"), ("int8", "int32")])
+def test_tensor_mn_major_operands(compute, a_order, b_order, kind, out_kind):
+    # column-major A and / or row-major B: the M- / N-contiguous operand layouts of the tensor path
+    # (the reference tensorizes every FIRST_MAJOR / LAST_MAJOR combination, mfma_tests.py:2797-2894)
+    _tensor_case(kind, out_kind, 256, 512, 256, compute, a_order=a_order, b_order=b_order)
+    _tensor_case(kind, out_kind, 304, 272, 208, compute, beta=1.0, a_order=a_order, b_order=b_order)
+
+
+def test_tf32_mn_major_is_refused_by_the_tensor_path_and_served_by_fp32_simt():
+    rng = np.random.default_rng(8)
+    A = np.asfortranarray(rng.standard_normal((128, 64), dtype=np.float32))
+    B = np.asfortranarray(rng.standard_normal((64, 96), dtype=np.float32))
+    C = np.zeros((128, 96), np.float32)
+    with pytest.raises(rt.AccbError):
+        rt.gemm(A, B, C, compute="tensor")
+    rt.gemm(A, B, C, compute="tensor_preferred")
+    np.testing.assert_allclose(C, A.astype(np.float64) @ B.astype(np.float64), rtol=1e-4, atol=1e-4)
