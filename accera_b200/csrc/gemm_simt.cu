@@ -352,6 +352,213 @@ bool f32_rr_ok(const GemmLaunch& g, const SimtParams& p)
            (reinterpret_cast<uintptr_t>(g.a) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.b) & 15) == 0 && p.k > 0;
 }
 
+// ---------------------------------------------------------------------------------
+// fp32, row-major A / B / C, 128 x 128 tile with 8 x 8 register tiles, optional split along K.
+//
+// With 2 x 4 register tiles the kernel above spends more cycles on shared-memory wavefronts than on FMAs;
+// 8 x 8 tiles balance the two, but a 512^3 problem then has only 16 tiles for 148 SMs.  So K is split over
+// a thread-block CLUSTER: the `splits` (1, 2, 4 or 8) CTAs of a cluster work on one output tile, each over
+// its own K range, park their partial tile in their own shared memory, and after a cluster barrier every
+// CTA folds 1/splits of the tile's rows by reading all the partials through distributed shared memory - in
+// split order, so the result does not depend on timing - applies the epilogue and writes C.  No global
+// workspace, no atomics.
+// ---------------------------------------------------------------------------------
+
+struct SplitKParams {
+    int splits;              // cluster size along z
+    int64_t k_per_split;     // multiple of 16
+};
+
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local_addr, uint32_t cta)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote));
+    return v;
+}
+
+__global__ void __launch_bounds__(256, 2)
+gemm_simt_f32_8x8_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                         const float* __restrict__ bias, SimtParams p, SplitKParams sk)
+{
+    constexpr int BM = 128, BN = 128, BK = 16, LDS_ = BM + 4;
+    // 64 KB: the k-tile buffers during the main loop (2 x 2 x 16 x 132 floats = 33 KB), the whole partial tile after it
+    extern __shared__ __align__(16) float smem_f[];
+    float (*As)[BK][LDS_] = reinterpret_cast<float (*)[BK][LDS_]>(smem_f);                       // As[2][k][m]
+    float (*Bs)[BK][LDS_] = reinterpret_cast<float (*)[BK][LDS_]>(smem_f + 2 * BK * LDS_);       // Bs[2][k][n]
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int64_t m0 = (int64_t)blockIdx.y * BM, n0 = (int64_t)blockIdx.x * BN;
+    const int split = blockIdx.z;                         // == rank in the cluster (cluster dims are 1 x 1 x splits)
+    const int64_t k_begin = (int64_t)split * sk.k_per_split;
+    const int64_t k_end = (k_begin + sk.k_per_split < p.k) ? k_begin + sk.k_per_split : p.k;
+    const int64_t kt_count = (k_end > k_begin) ? (k_end - k_begin + BK - 1) / BK : 0;
+
+    float4 ra[2], rb[2];
+    auto fetch = [&](int64_t k0) {
+#pragma unroll
+        for (int l = 0; l < 2; ++l) {
+            const int idx = tid + l * 256;
+            const int mm = idx >> 2, kq = (idx & 3) * 4;                  // A: 128 rows x 4 float4 along k
+            const int64_t gm = m0 + mm, gk = k0 + kq;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (gm < p.m && gk < k_end) {
+                const float* src = A + gm * p.as0 + gk;
+                if (gk + 4 <= k_end) v = *reinterpret_cast<const float4*>(src);
+                else { v.x = src[0]; if (gk + 1 < k_end) v.y = src[1]; if (gk + 2 < k_end) v.z = src[2]; }
+            }
+            ra[l] = v;
+            const int kk = idx >> 5, nq = (idx & 31) * 4;                 // B: 16 rows x 32 float4 along n
+            const int64_t gk2 = k0 + kk, gn = n0 + nq;
+            float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (gk2 < k_end && gn < p.n) {
+                const float* src = B + gk2 * p.bs0 + gn;
+                if (gn + 4 <= p.n) w = *reinterpret_cast<const float4*>(src);
+                else { w.x = src[0]; if (gn + 1 < p.n) w.y = src[1]; if (gn + 2 < p.n) w.z = src[2]; }
+            }
+            rb[l] = w;
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int l = 0; l < 2; ++l) {
+            const int idx = tid + l * 256;
+            const int mm = idx >> 2, kq = (idx & 3) * 4;
+            As[buf][kq + 0][mm] = ra[l].x; As[buf][kq + 1][mm] = ra[l].y;
+            As[buf][kq + 2][mm] = ra[l].z; As[buf][kq + 3][mm] = ra[l].w;
+            const int kk = idx >> 5, nq = (idx & 31) * 4;
+            *reinterpret_cast<float4*>(&Bs[buf][kk][nq]) = rb[l];
+        }
+    };
+
+    // this thread's 8 rows are ty*4 .. +3 and 64 + ty*4 .. +3, its 8 columns tx*4 .. +3 and 64 + tx*4 .. +3:
+    // the two 4-wide halves keep every 128-bit shared-memory load of a warp phase inside one 128-byte line
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+    if (kt_count > 0) { fetch(k_begin); stash(0); }
+    __syncthreads();
+    for (int64_t kt = 0; kt < kt_count; ++kt) {
+        const int buf = (int)(kt & 1);
+        const bool more = kt + 1 < kt_count;
+        if (more) fetch(k_begin + (kt + 1) * BK);
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
+            const float av[8] = { a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w };
+            const float bv[8] = { b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w };
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] += av[i] * bv[j];
+        }
+        if (more) stash(buf ^ 1);
+        __syncthreads();
+    }
+
+    const bool c_vec = (p.cs0 % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+    auto finish4 = [&](float4 v4, int64_t gm, int64_t gn) {          // epilogue + store of 4 consecutive columns
+        if (gm >= p.m || gn >= p.n) return;
+        float* dst = C + gm * p.cs0 + gn;
+        const int ncols = (int)(p.n - gn >= 4 ? 4 : p.n - gn);
+        float v[4] = { v4.x, v4.y, v4.z, v4.w };
+        float old[4] = { 0.f, 0.f, 0.f, 0.f };
+        if (p.beta != 0.0f) {
+            if (c_vec && ncols == 4) { const float4 o = *reinterpret_cast<const float4*>(dst); old[0] = o.x; old[1] = o.y; old[2] = o.z; old[3] = o.w; }
+            else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) if (j < ncols) old[j] = dst[j];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float x = v[j];
+            if (p.alpha == 1.0f) {
+                if (p.beta == 1.0f) x += old[j];
+                else if (p.beta != 0.0f) x += p.beta * old[j];
+            } else {
+                x *= p.alpha;
+                if (p.beta != 0.0f) x += p.beta * old[j];
+            }
+            if (bias && j < ncols) x += bias[gn + j];
+            if (p.relu) x = fmaxf(x, 0.0f);
+            v[j] = x;
+        }
+        if (c_vec && ncols == 4) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) if (j < ncols) dst[j] = v[j];
+        }
+    };
+
+    if (sk.splits == 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int64_t gm = m0 + ((i < 4) ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+            finish4(make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]), gm, n0 + tx * 4);
+            finish4(make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]), gm, n0 + 64 + tx * 4);
+        }
+        return;
+    }
+
+    // park the partial tile in shared memory, row-major [128][128] (the k-tile buffers are no longer needed:
+    // the loop above ended with a __syncthreads)
+    float* part = smem_f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = (i < 4) ? ty * 4 + i : 64 + ty * 4 + (i - 4);
+        *reinterpret_cast<float4*>(part + r * BN + tx * 4) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        *reinterpret_cast<float4*>(part + r * BN + 64 + tx * 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    // CTA `split` folds rows [split * 128 / splits, (split + 1) * 128 / splits) of the tile
+    const int rows_per = BM / sk.splits;
+    const int vec_count = rows_per * (BN / 4);
+    const uint32_t part_addr = (uint32_t)__cvta_generic_to_shared(part);
+    for (int v = tid; v < vec_count; v += 256) {
+        const int r = split * rows_per + v / (BN / 4), c4 = v % (BN / 4);
+        const uint32_t off = (uint32_t)((r * BN + c4 * 4) * sizeof(float));
+        float4 q[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) if (s < sk.splits) q[s] = ld_dsmem_f4(part_addr + off, (uint32_t)s);
+        float4 sum = q[0];
+#pragma unroll
+        for (int s = 1; s < 8; ++s)
+            if (s < sk.splits) { sum.x += q[s].x; sum.y += q[s].y; sum.z += q[s].z; sum.w += q[s].w; }   // fixed order
+        finish4(sum, m0 + r, n0 + c4 * 4);
+    }
+    // no CTA may leave while another one is still reading its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// How the 8 x 8 kernel would be launched for this problem: number of K splits (1 = no split)
+struct SplitPlan { int splits; int64_t k_per_split; int64_t tiles; bool use; };
+
+SplitPlan plan_8x8(const SimtParams& p, int num_sms)
+{
+    SplitPlan sp{1, 0, 0, false};
+    const int64_t tiles = ((p.m + 127) / 128) * ((p.n + 127) / 128);
+    sp.tiles = tiles;
+    if (p.k < 16 || (p.m + 127) / 128 > 65535) return sp;
+    sp.k_per_split = (p.k + 15) / 16 * 16;
+    if (tiles >= 2 * (int64_t)num_sms) { sp.use = true; return sp; }       // big: no split
+    // small: the largest power-of-two split (<= 8, >= 64 of K each) that does not overfill two CTAs per SM
+    int s = 1;
+    while (s < 8 && tiles * (s * 2) <= 2 * (int64_t)num_sms && p.k / (s * 2) >= 64) s *= 2;
+    sp.splits = s;
+    sp.k_per_split = ((p.k + s - 1) / s + 15) / 16 * 16;
+    // worth it only if the grid is then reasonably full; otherwise the smaller-tile kernel does better
+    sp.use = tiles * s >= num_sms / 2;
+    return sp;
+}
+
 template <typename TA, typename TB, typename TC, typename ACC>
 cudaError_t launch_typed(const GemmLaunch& g, const SimtParams& p)
 {
@@ -388,7 +595,26 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err)
     cudaError_t e;
     const int a = d.a_type, b = d.b_type, c = d.c_type;
     if (a == ACCB_F32 && b == ACCB_F32 && c == ACCB_F32) {
-        if (f32_rr_ok(g, p)) {
+        const SplitPlan sp = f32_rr_ok(g, p) ? plan_8x8(p, g.num_sms) : SplitPlan{1, 0, 0, false};
+        if (sp.use) {
+            SplitKParams sk;
+            sk.splits = sp.splits;
+            sk.k_per_split = sp.k_per_split;
+            constexpr int kSmem = 128 * 128 * (int)sizeof(float);
+            e = cudaFuncSetAttribute(gemm_simt_f32_8x8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+            if (e == cudaSuccess) {
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3((unsigned)((p.n + 127) / 128), (unsigned)((p.m + 127) / 128), (unsigned)sp.splits);
+                cfg.blockDim = dim3(256);
+                cfg.dynamicSmemBytes = kSmem;
+                cfg.stream = g.stream;
+                cudaLaunchAttribute attr[1];
+                attr[0].id = cudaLaunchAttributeClusterDimension;
+                attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)sp.splits;
+                cfg.attrs = attr; cfg.numAttrs = 1;
+                e = cudaLaunchKernelEx(&cfg, gemm_simt_f32_8x8_kernel, (const float*)g.a, (const float*)g.b, (float*)g.c, g.bias, p, sk);
+            }
+        } else if (f32_rr_ok(g, p)) {
             const int64_t tiles64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
             if (tiles64 >= 2 * (int64_t)g.num_sms) e = launch_f32_rr<64, 64, 32, 4, 4, 3>(g, p);
             else e = launch_f32_rr<32, 64, 32, 2, 4, 4>(g, p);       // small problems: more, smaller tiles

@@ -258,8 +258,8 @@ def extras_single_gpu(device, peaks):
     b = 2 * 16384 * 4096 * 4 + 16384 * 8
     out["gather_f32_32000x4096_idx16384"] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
     del T, idxs, outs
-    A = torch.rand(512, 512, device=device); B = torch.rand(512, 512, device=device); C = torch.zeros(512, 512, device=device)
-    t = timeit([lambda: rt.gemm(A, B, C, relu=True, compute="simt")])            # 3 MiB: L2 resident by nature
+    A1 = torch.rand(512, 512, device=device); B1 = torch.rand(512, 512, device=device); C1 = torch.zeros(512, 512, device=device)
+    t = timeit([lambda: rt.gemm(A1, B1, C1, relu=True, compute="simt")])            # 3 MiB: L2 resident by nature
     out["matmul_relu_f32_simt_512"] = {"us": t * 1e6, "TFLOP/s": 2 * 512 ** 3 / t / 1e12}
     A = (torch.rand(4096, 4096, device=device) * 2 - 1).half(); B = (torch.rand(4096, 4096, device=device) * 2 - 1).half().t()
     C = torch.zeros(4096, 4096, device=device)
@@ -272,6 +272,30 @@ def extras_single_gpu(device, peaks):
     t = timeit([lambda: rt.gemm(A, B, C, compute="tensor_2sm")], iters=20)
     out["gemm_s8_s32_8192"] = {"us": t * 1e6, "TOP/s": 2 * 8192 ** 3 / t / 1e12,
                                "frac_nominal_int8_peak(2x measured bf16)": 2 * 8192 ** 3 / t / 1e12 / (2 * peaks["bf16_tflops"])}
+    try:
+        # the same launches replayed from a CUDA graph: at ~10 us per launch the Python / driver launch path
+        # above is slower than the kernel, the graph shows the device time
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            rt.gemm(A1, B1, C1, relu=True, compute="simt")          # first call on this stream: allocates its split-K workspace
+            torch.cuda.synchronize(device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(20):
+                    rt.gemm(A1, B1, C1, relu=True, compute="simt")
+            graph.replay()
+            torch.cuda.synchronize(device)
+            s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s_ev.record(side)
+            for _ in range(5):
+                graph.replay()
+            e_ev.record(side)
+            torch.cuda.synchronize(device)
+            tg = s_ev.elapsed_time(e_ev) * 1e-3 / 100
+        out["matmul_relu_f32_simt_512"].update({"us_cuda_graph": tg * 1e6, "TFLOP/s_cuda_graph": 2 * 512 ** 3 / tg / 1e12})
+    except Exception as exc:                                   # reported beside the number, never fatal
+        out["matmul_relu_f32_simt_512"]["cuda_graph"] = f"not measured: {exc!r}"
     return out
 
 

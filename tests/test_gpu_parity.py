@@ -601,3 +601,21 @@ def test_tf32_mn_major_is_refused_by_the_tensor_path_and_served_by_fp32_simt():
         rt.gemm(A, B, C, compute="tensor")
     rt.gemm(A, B, C, compute="tensor_preferred")
     np.testing.assert_allclose(C, A.astype(np.float64) @ B.astype(np.float64), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 512, 512), (256, 384, 1000), (1024, 1024, 1024), (130, 260, 4096), (128, 128, 64),
+                                   (2304, 2304, 96)])
+def test_simt_f32_8x8_tiles_and_split_k(m, n, k):
+    # row-major fp32: 128 x 128 tiles with 8 x 8 register tiles; small problems are split along K and the
+    # partial tiles are folded in a fixed order, so two runs give bit-identical results
+    rng = np.random.default_rng(m * 3 + n * 5 + k)
+    A = rng.standard_normal((m, k), dtype=np.float32)
+    B = rng.standard_normal((k, n), dtype=np.float32)
+    C0 = rng.standard_normal((m, n), dtype=np.float32)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    want = oracle.gemm(A, B, C0.copy(), bias=bias, relu=True)
+    got1, got2 = C0.copy(), C0.copy()
+    rt.gemm(A, B, got1, bias=bias, relu=True, compute="simt")
+    rt.gemm(A, B, got2, bias=bias, relu=True, compute="simt")
+    _assert_close(got1, want, _gemm_scale(A, B) + np.abs(C0) + np.abs(bias), RTOL_F32, f"simt 8x8 {m}x{n}x{k}")
+    assert np.array_equal(got1, got2)
