@@ -147,29 +147,41 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     return mbar_wait_slow(bar, parity, status, site, detail);
 }
 
+// L2 eviction-priority policy for the operand loads; 0 = none (the plain load form is used)
 __device__ __forceinline__ uint64_t make_l2_policy(int hint)
 {
-    uint64_t pol;
+    uint64_t pol = 0;
     if (hint == 1) asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
     else if (hint == 2) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-    else asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
     return pol;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, uint64_t pol)
 {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "l"(pol)
-        : "memory");
+    if (pol == 0)
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+            : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "l"(pol)
+            : "memory");
 }
 // CTA-pair form: the transaction bytes are signalled on the barrier of the pair's rank-0 CTA
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, uint64_t pol)
 {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & kPeerMask), "r"(c0), "r"(c1), "l"(pol)
-        : "memory");
+    if (pol == 0)
+        asm volatile(
+            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & kPeerMask), "r"(c0), "r"(c1)
+            : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & kPeerMask), "r"(c0), "r"(c1), "l"(pol)
+            : "memory");
 }
 
 // TMA store of one shared-memory box into a C replica (rows / columns outside the tensor are clipped)
@@ -564,6 +576,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int unit = (int)blockIdx.x / kCtas;
     const int slab_elems = kSlabBytes / p.elem_bytes;
     const int num_kb = (int)((p.k + slab_elems - 1) / slab_elems);
+    const bool k_major_both = !p.a_mn && !p.b_mn;
+    const uint32_t mn_block = (uint32_t)(kSlabBytes * slab_elems);                      // bytes of one MN-major box
+    const uint32_t mn_step = (uint32_t)((kMmaKBytes / p.elem_bytes) * kSlabBytes);      // bytes one MMA advances in it
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -599,24 +614,35 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     } else {
                         mbar_arrive_expect_tx(full_bar(s), (uint32_t)Plan::kStageBytes);
                     }
-                    auto load = [&](uint32_t dst, const CUtensorMap* map, int c0, int c1, uint64_t pol) {
-                        if constexpr (TWO_SM) tma_load_2d_pair(dst, map, full_bar(s), c0, c1, pol);
-                        else tma_load_2d(dst, map, full_bar(s), c0, c1, pol);
-                    };
-                    // K-major operand: one box [rows][128 B of K].  MN-major operand: one box [k rows][128 B of MN]
-                    // per 128-byte block of the tile's MN extent, stacked in shared memory.
-                    if (!p.a_mn) {
-                        load(sa, &map_a, kb * slab_elems, row_a, pol_a);
+                    if (k_major_both) {
+                        // both operands K-contiguous: one box [rows][128 B of K] each
+                        if constexpr (TWO_SM) {
+                            tma_load_2d_pair(sa, &map_a, full_bar(s), kb * slab_elems, row_a, pol_a);
+                            tma_load_2d_pair(sb, &map_b, full_bar(s), kb * slab_elems, row_b, pol_b);
+                        } else {
+                            tma_load_2d(sa, &map_a, full_bar(s), kb * slab_elems, row_a, pol_a);
+                            tma_load_2d(sb, &map_b, full_bar(s), kb * slab_elems, row_b, pol_b);
+                        }
                     } else {
-                        for (int blk = 0; blk < kBlockM / slab_elems; ++blk)
-                            load(sa + blk * (kSlabBytes * slab_elems), &map_a, row_a + blk * slab_elems, kb * slab_elems, pol_a);
-                    }
-                    constexpr int kRowsB = TWO_SM ? kBlockN / 2 : kBlockN;
-                    if (!p.b_mn) {
-                        load(sb, &map_b, kb * slab_elems, row_b, pol_b);
-                    } else {
-                        for (int blk = 0; blk < kRowsB / slab_elems; ++blk)
-                            load(sb + blk * (kSlabBytes * slab_elems), &map_b, row_b + blk * slab_elems, kb * slab_elems, pol_b);
+                        auto load = [&](uint32_t dst, const CUtensorMap* map, int c0, int c1, uint64_t pol) {
+                            if constexpr (TWO_SM) tma_load_2d_pair(dst, map, full_bar(s), c0, c1, pol);
+                            else tma_load_2d(dst, map, full_bar(s), c0, c1, pol);
+                        };
+                        // MN-major operand: one box [k rows][128 B of MN] per 128-byte block of the tile's MN
+                        // extent, stacked in shared memory
+                        if (!p.a_mn) {
+                            load(sa, &map_a, kb * slab_elems, row_a, pol_a);
+                        } else {
+                            for (int blk = 0; blk < kBlockM / slab_elems; ++blk)
+                                load(sa + blk * (kSlabBytes * slab_elems), &map_a, row_a + blk * slab_elems, kb * slab_elems, pol_a);
+                        }
+                        constexpr int kRowsB = TWO_SM ? kBlockN / 2 : kBlockN;
+                        if (!p.b_mn) {
+                            load(sb, &map_b, kb * slab_elems, row_b, pol_b);
+                        } else {
+                            for (int blk = 0; blk < kRowsB / slab_elems; ++blk)
+                                load(sb + blk * (kSlabBytes * slab_elems), &map_b, row_b + blk * slab_elems, kb * slab_elems, pol_b);
+                        }
                     }
                 }
                 if (p.pace_pct > 0 && leader && ok) atomicAdd(p.pace, 1);   // counted even after this CTA stopped waiting
@@ -641,18 +667,27 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t sa = smem_base + s * Plan::kStageBytes;
                     const uint32_t sb = sa + Plan::kABytes;
-                    // K-major: advancing K inside the swizzle atom is +32 bytes on the start address.
-                    // MN-major: one MMA consumes (32 / elem_bytes) k-rows of 128 bytes each.
-                    const uint32_t mn_block = (uint32_t)(kSlabBytes * slab_elems);
-                    const uint32_t mn_step = (uint32_t)((kMmaKBytes / p.elem_bytes) * kSlabBytes);
-                    const uint64_t adesc = p.a_mn ? make_smem_desc_mn(sa, mn_block) : make_smem_desc(sa);
-                    const uint64_t bdesc = p.b_mn ? make_smem_desc_mn(sb, mn_block) : make_smem_desc(sb);
-                    const uint64_t astep = (uint64_t)((p.a_mn ? mn_step : (uint32_t)kMmaKBytes) >> 4);
-                    const uint64_t bstep = (uint64_t)((p.b_mn ? mn_step : (uint32_t)kMmaKBytes) >> 4);
+                    if (k_major_both) {
+                        // advancing K inside the swizzle atom: +32 bytes on the start address (16-byte units)
+                        const uint64_t adesc = make_smem_desc(sa);
+                        const uint64_t bdesc = make_smem_desc(sb);
 #pragma unroll
-                    for (int j = 0; j < kSlabBytes / kMmaKBytes; ++j) {
-                        umma<KIND, TWO_SM>(tmem_d, adesc + (uint64_t)j * astep, bdesc + (uint64_t)j * bstep, p.idesc,
-                                           (kb > 0 || j > 0) ? 1u : 0u);
+                        for (int j = 0; j < kSlabBytes / kMmaKBytes; ++j) {
+                            umma<KIND, TWO_SM>(tmem_d, adesc + (uint64_t)(j * (kMmaKBytes >> 4)),
+                                               bdesc + (uint64_t)(j * (kMmaKBytes >> 4)), p.idesc,
+                                               (kb > 0 || j > 0) ? 1u : 0u);
+                        }
+                    } else {
+                        // MN-major operand: one MMA consumes (32 / elem_bytes) k-rows of 128 bytes each
+                        const uint64_t adesc = p.a_mn ? make_smem_desc_mn(sa, mn_block) : make_smem_desc(sa);
+                        const uint64_t bdesc = p.b_mn ? make_smem_desc_mn(sb, mn_block) : make_smem_desc(sb);
+                        const uint64_t astep = (uint64_t)((p.a_mn ? mn_step : (uint32_t)kMmaKBytes) >> 4);
+                        const uint64_t bstep = (uint64_t)((p.b_mn ? mn_step : (uint32_t)kMmaKBytes) >> 4);
+#pragma unroll
+                        for (int j = 0; j < kSlabBytes / kMmaKBytes; ++j) {
+                            umma<KIND, TWO_SM>(tmem_d, adesc + (uint64_t)j * astep, bdesc + (uint64_t)j * bstep, p.idesc,
+                                               (kb > 0 || j > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit<TWO_SM>(empty_bar(s));            // frees the stage once these MMAs have read it
                 }
