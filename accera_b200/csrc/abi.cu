@@ -180,17 +180,17 @@ int dispatch_gemm(const GemmLaunch& g, const char** err)
     const accb_gemm_desc& d = g.d;
     if (d.k == 0) return launch_gemm_simt(g, err);          // nothing to accumulate: epilogue of beta * C
     if (d.compute == ACCB_COMPUTE_SIMT) return launch_gemm_simt(g, err);
-    if (d.compute == ACCB_COMPUTE_TENSOR) return launch_gemm_umma(g, false, err);
-    if (d.compute == ACCB_COMPUTE_TENSOR_2SM) return launch_gemm_umma(g, true, err);
+    if (d.compute == ACCB_COMPUTE_TENSOR) return launch_gemm_umma(g, 0, err);
+    if (d.compute == ACCB_COMPUTE_TENSOR_2SM) return launch_gemm_umma(g, 1, err);
     if (d.compute == ACCB_COMPUTE_TENSOR_PREFERRED) {
         const char* why = nullptr;
-        if (gemm_umma_supported(g, &why)) return launch_gemm_umma(g, d.m > 128, err);
+        if (gemm_umma_supported(g, &why)) return launch_gemm_umma(g, d.m > 128 ? -1 : 0, err);
         return launch_gemm_simt(g, err);
     }
     // AUTO: fp32 inputs stay on the bit-faithful fp32 path; narrower inputs take the tensor cores when the
     // layout allows it (CTA pairs as soon as there is more than one 128-row tile) and the SIMT kernel otherwise
     const char* why = nullptr;
-    if (d.a_type != ACCB_F32 && gemm_umma_supported(g, &why)) return launch_gemm_umma(g, d.m > 128, err);
+    if (d.a_type != ACCB_F32 && gemm_umma_supported(g, &why)) return launch_gemm_umma(g, d.m > 128 ? -1 : 0, err);
     return launch_gemm_simt(g, err);
 }
 
@@ -226,7 +226,7 @@ int pipelined_host_gemm(DeviceState& s, GemmLaunch g, const void* a, const void*
         const size_t off_c = (size_t)r0 * d.c_stride[0] * ec, len_c = ((size_t)(rows - 1) * d.c_stride[0] + d.n) * ec;
         if (idx & 1) e = cudaStreamWaitEvent(st, s.pipe_ready, 0);
         if (e == cudaSuccess) e = cudaMemcpyAsync((char*)s.slot[0] + off_a, (const char*)a + off_a, len_a, cudaMemcpyHostToDevice, st);
-        if (e == cudaSuccess && d.beta != 0.0f)
+        if (e == cudaSuccess && (d.beta != 0.0f || d.c_stride[0] != d.n))     // padded rows: keep the caller's bytes in the gaps
             e = cudaMemcpyAsync((char*)s.slot[2] + off_c, (const char*)c + off_c, len_c, cudaMemcpyHostToDevice, st);
         if (e != cudaSuccess) return fail_cuda("host to device copy", e);
         GemmLaunch part = g;
@@ -258,22 +258,28 @@ using namespace accb;
 
 extern "C" {
 
-int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c, const float* bias)
+// One entry for accb_gemm (batch = 1, `fn` names the caller in error texts) and accb_gemm_batched.
+static int gemm_entry(const char* fn, const accb_gemm_desc* desc, int64_t batch, int64_t a_bs, int64_t b_bs, int64_t c_bs,
+                      const void* a, const void* b, void* c, const float* bias)
 {
     t_error.clear();
-    if (!desc) return fail(ACCB_ERR_ARG, "accb_gemm: null descriptor");
+    const std::string who = std::string(fn) + ": ";
+    if (!desc) return fail(ACCB_ERR_ARG, who + "null descriptor");
     const accb_gemm_desc& d = *desc;
-    if (d.m < 0 || d.n < 0 || d.k < 0) return fail(ACCB_ERR_ARG, "accb_gemm: negative dimension");
+    if (d.m < 0 || d.n < 0 || d.k < 0) return fail(ACCB_ERR_ARG, who + "negative dimension");
     const size_t ea = type_bytes(d.a_type), eb = type_bytes(d.b_type), ec = type_bytes(d.c_type);
-    if (!ea || !eb || !ec) return fail(ACCB_ERR_ARG, "accb_gemm: unknown element type");
+    if (!ea || !eb || !ec) return fail(ACCB_ERR_ARG, who + "unknown element type");
     for (int i = 0; i < 2; ++i)
         if (d.a_stride[i] < 1 || d.b_stride[i] < 1 || d.c_stride[i] < 1)
-            return fail(ACCB_ERR_ARG, "accb_gemm: strides must be positive");
-    if (d.epilogue != ACCB_EPI_NONE && d.epilogue != ACCB_EPI_RELU) return fail(ACCB_ERR_ARG, "accb_gemm: unknown epilogue");
-    if (d.compute < ACCB_COMPUTE_AUTO || d.compute > ACCB_COMPUTE_TENSOR_PREFERRED) return fail(ACCB_ERR_ARG, "accb_gemm: unknown compute mode");
-    if (d.max_ctas < 0) return fail(ACCB_ERR_ARG, "accb_gemm: max_ctas must be >= 0");
-    if (d.m == 0 || d.n == 0) return ACCB_OK;
-    if (!a || !b || !c) return fail(ACCB_ERR_ARG, "accb_gemm: null array pointer");
+            return fail(ACCB_ERR_ARG, who + "strides must be positive");
+    if (d.epilogue != ACCB_EPI_NONE && d.epilogue != ACCB_EPI_RELU) return fail(ACCB_ERR_ARG, who + "unknown epilogue");
+    if (d.compute < ACCB_COMPUTE_AUTO || d.compute > ACCB_COMPUTE_TENSOR_PREFERRED) return fail(ACCB_ERR_ARG, who + "unknown compute mode");
+    if (d.max_ctas < 0) return fail(ACCB_ERR_ARG, who + "max_ctas must be >= 0");
+    if (batch < 0 || a_bs < 0 || b_bs < 0 || c_bs < 0) return fail(ACCB_ERR_ARG, who + "negative batch count or batch stride");
+    if (d.m == 0 || d.n == 0 || batch == 0) return ACCB_OK;
+    if (batch > 1 && c_bs < span_elems(d.m, d.n, d.c_stride))
+        return fail(ACCB_ERR_ARG, who + "c_batch_stride is smaller than one C: the problems' results would overlap");
+    if (!a || !b || !c) return fail(ACCB_ERR_ARG, who + "null array pointer");
 
     DeviceState* sp = nullptr;
     int dev = 0;
@@ -285,19 +291,28 @@ int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c,
     const bool dev_bias = bias ? is_device_pointer(bias) : dev_c;
     const bool all_dev = dev_a && dev_b && dev_c && dev_bias;
     const bool all_host = !dev_a && !dev_b && !dev_c && (bias ? !dev_bias : true);
-    if (!all_dev && !all_host) return fail(ACCB_ERR_ARG, "accb_gemm: mix of host and device pointers");
+    if (!all_dev && !all_host) return fail(ACCB_ERR_ARG, who + "mix of host and device pointers");
 
     GemmLaunch g;
     g.d = d;
     g.n_extra_c = 0;
+    g.batch = batch;
+    g.a_batch_stride = batch > 1 ? a_bs : 0;
+    g.b_batch_stride = batch > 1 ? b_bs : 0;
+    g.c_batch_stride = batch > 1 ? c_bs : 0;
     g.stream = t_stream;
     g.status = s.status;
     g.device = dev;
     g.num_sms = s.num_sms;
 
-    const size_t bytes_a = (size_t)span_elems(d.m, d.k, d.a_stride) * ea;
-    const size_t bytes_b = (size_t)span_elems(d.k, d.n, d.b_stride) * eb;
-    const size_t bytes_c = (size_t)span_elems(d.m, d.n, d.c_stride) * ec;
+    // bytes from the base pointer to the end of the last problem's array
+    auto span_bytes = [&](int64_t d0, int64_t d1, const int64_t* st, int64_t bs, size_t es) -> size_t {
+        const int64_t one = span_elems(d0, d1, st);
+        return one ? (size_t)((batch - 1) * (batch > 1 ? bs : 0) + one) * es : 0;
+    };
+    const size_t bytes_a = span_bytes(d.m, d.k, d.a_stride, a_bs, ea);
+    const size_t bytes_b = span_bytes(d.k, d.n, d.b_stride, b_bs, eb);
+    const size_t bytes_c = span_bytes(d.m, d.n, d.c_stride, c_bs, ec);
 
     std::unique_lock<std::mutex> lock(s.mu, std::defer_lock);
     if (all_host) {
@@ -307,12 +322,15 @@ int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c,
         if ((rc = ensure(&s.slot[2], &s.slot_bytes[2], bytes_c)) != ACCB_OK) return rc;
         if (bias && (rc = ensure(&s.slot[3], &s.slot_bytes[3], (size_t)d.n * 4)) != ACCB_OK) return rc;
         const bool row_major_ac = d.a_stride[1] == 1 && d.c_stride[1] == 1 && d.a_stride[0] >= d.k && d.c_stride[0] >= d.n;
-        if (row_major_ac && d.m >= 4096 && d.k > 0 && bytes_a + bytes_c >= ((size_t)64 << 20))
+        if (batch == 1 && row_major_ac && d.m >= 4096 && d.k > 0 && bytes_a + bytes_c >= ((size_t)64 << 20))
             return pipelined_host_gemm(s, g, a, b, c, bias, ea, ec, bytes_b);
         cudaError_t e = cudaSuccess;
         if (bytes_a) e = cudaMemcpyAsync(s.slot[0], a, bytes_a, cudaMemcpyHostToDevice, g.stream);
         if (e == cudaSuccess && bytes_b) e = cudaMemcpyAsync(s.slot[1], b, bytes_b, cudaMemcpyHostToDevice, g.stream);
-        if (e == cudaSuccess && d.beta != 0.0f) e = cudaMemcpyAsync(s.slot[2], c, bytes_c, cudaMemcpyHostToDevice, g.stream);
+        // C goes to the device when it is read (beta != 0) and also when it has gaps (padded rows or problems):
+        // the copy back covers the whole extent, so the gaps must carry the caller's bytes
+        const bool c_dense = bytes_c == (size_t)batch * (size_t)d.m * (size_t)d.n * ec;
+        if (e == cudaSuccess && (d.beta != 0.0f || !c_dense)) e = cudaMemcpyAsync(s.slot[2], c, bytes_c, cudaMemcpyHostToDevice, g.stream);
         if (e == cudaSuccess && bias) e = cudaMemcpyAsync(s.slot[3], bias, (size_t)d.n * 4, cudaMemcpyHostToDevice, g.stream);
         if (e != cudaSuccess) return fail_cuda("host to device copy", e);
         g.a = s.slot[0]; g.b = s.slot[1]; g.c = s.slot[2]; g.bias = bias ? (const float*)s.slot[3] : nullptr;
@@ -322,7 +340,7 @@ int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c,
 
     const char* err = "";
     const int n = dispatch_gemm(g, &err);
-    if (n < 0) return fail(n, std::string("accb_gemm: ") + err);
+    if (n < 0) return fail(n, who + err);
 
     if (all_host) {
         cudaError_t e = cudaMemcpyAsync(c, s.slot[2], bytes_c, cudaMemcpyDeviceToHost, g.stream);
@@ -330,6 +348,17 @@ int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c,
         return collect_status(s, g.stream);
     }
     return ACCB_OK;
+}
+
+int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c, const float* bias)
+{
+    return gemm_entry("accb_gemm", desc, 1, 0, 0, 0, a, b, c, bias);
+}
+
+int accb_gemm_batched(const accb_gemm_desc* desc, int64_t batch, int64_t a_batch_stride, int64_t b_batch_stride,
+                      int64_t c_batch_stride, const void* a, const void* b, void* c, const float* bias)
+{
+    return gemm_entry("accb_gemm_batched", desc, batch, a_batch_stride, b_batch_stride, c_batch_stride, a, b, c, bias);
 }
 
 int accb_gemm_replicated(const accb_gemm_desc* desc, const void* a, const void* b, void* const* c_replicas,
@@ -363,7 +392,7 @@ int accb_gemm_replicated(const accb_gemm_desc* desc, const void* a, const void* 
     g.device = dev;
     g.num_sms = sp->num_sms;
     const char* err = "";
-    const int n = launch_gemm_umma(g, d.compute != ACCB_COMPUTE_TENSOR, &err);
+    const int n = launch_gemm_umma(g, d.compute != ACCB_COMPUTE_TENSOR ? 1 : 0, &err);
     if (n < 0) return fail(n, std::string("accb_gemm_replicated: ") + err);
     return ACCB_OK;
 }

@@ -32,6 +32,10 @@ struct GemmLaunch {
     // only the tensor-core path with a TMA-storable C supports them
     void* extra_c[7];
     int n_extra_c;
+    // batched GEMM: `batch` independent problems of the same shape; operand i of problem b starts
+    // b * *_batch_stride elements after the base (a stride of 0 shares that operand between all problems)
+    int64_t batch = 1;
+    int64_t a_batch_stride = 0, b_batch_stride = 0, c_batch_stride = 0;
     cudaStream_t stream;
     int* status;       // device pointer to kStatusWords ints
     int device;
@@ -43,7 +47,8 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err);
 
 // gemm_umma.cu: tcgen05/TMEM path. `supported` explains in *why when it returns false.
 bool gemm_umma_supported(const GemmLaunch& g, const char** why);
-int launch_gemm_umma(const GemmLaunch& g, bool two_sm, const char** err);
+// want_two_sm: 1 = CTA pairs (cta_group::2), 0 = single CTAs, -1 = whichever tile shape suits the problem.
+int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err);
 
 // reduce_mean.cu
 // Scratch (fp32 partial sums) a launch needs for these dims, in bytes; 0 when the

@@ -29,6 +29,7 @@ struct SimtParams {
     int64_t as0, as1, bs0, bs1, cs0, cs1;
     float alpha, beta;
     int relu;
+    int64_t a_bs, b_bs, c_bs;   // batched GEMM: element offsets between consecutive problems (blockIdx.z walks them)
 };
 
 template <typename ACC, typename T>
@@ -70,6 +71,9 @@ gemm_simt_kernel(const TA* __restrict__ A, const TB* __restrict__ B, TC* __restr
     const int ty = tid / (BN / TN);
     const int64_t m0 = (int64_t)blockIdx.y * BM;
     const int64_t n0 = (int64_t)blockIdx.x * BN;
+    A += (int64_t)blockIdx.z * p.a_bs;
+    B += (int64_t)blockIdx.z * p.b_bs;
+    C += (int64_t)blockIdx.z * p.c_bs;
 
     // Walk the tile along whichever dimension is contiguous in global memory so
     // that consecutive threads read consecutive addresses.
@@ -217,6 +221,9 @@ gemm_simt_f32_rr_kernel(const float* __restrict__ A, const float* __restrict__ B
     const int64_t m0 = (int64_t)blockIdx.y * BM;
     const int64_t n0 = (int64_t)blockIdx.x * BN;
     const int64_t kt_count = (p.k + BK - 1) / BK;
+    A += (int64_t)blockIdx.z * p.a_bs;
+    B += (int64_t)blockIdx.z * p.b_bs;
+    C += (int64_t)blockIdx.z * p.c_bs;
 
     auto load_stage = [&](int stage, int64_t kt) {
         const int64_t k0 = kt * BK;
@@ -340,7 +347,7 @@ cudaError_t launch_f32_rr(const GemmLaunch& g, const SimtParams& p)
     auto kernel = gemm_simt_f32_rr_kernel<BM, BN, BK, TM, TN, STAGES>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)((p.m + BM - 1) / BM));
+    dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)((p.m + BM - 1) / BM), (unsigned)g.batch);
     kernel<<<grid, NT, smem, g.stream>>>((const float*)g.a, (const float*)g.b, (float*)g.c, g.bias, p);
     return cudaGetLastError();
 }
@@ -349,6 +356,7 @@ cudaError_t launch_f32_rr(const GemmLaunch& g, const SimtParams& p)
 bool f32_rr_ok(const GemmLaunch& g, const SimtParams& p)
 {
     return p.as1 == 1 && p.bs1 == 1 && p.cs1 == 1 && p.as0 % 4 == 0 && p.bs0 % 4 == 0 &&
+           p.a_bs % 4 == 0 && p.b_bs % 4 == 0 &&
            (reinterpret_cast<uintptr_t>(g.a) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.b) & 15) == 0 && p.k > 0;
 }
 
@@ -390,7 +398,12 @@ gemm_simt_f32_8x8_kernel(const float* __restrict__ A, const float* __restrict__ 
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
     const int64_t m0 = (int64_t)blockIdx.y * BM, n0 = (int64_t)blockIdx.x * BN;
-    const int split = blockIdx.z;                         // == rank in the cluster (cluster dims are 1 x 1 x splits)
+    // blockIdx.z = problem * splits + split; clusters are 1 x 1 x splits, so `split` is also the rank in the cluster
+    const int split = (int)(blockIdx.z % (unsigned)sk.splits);
+    const int64_t problem = (int64_t)(blockIdx.z / (unsigned)sk.splits);
+    A += problem * p.a_bs;
+    B += problem * p.b_bs;
+    C += problem * p.c_bs;
     const int64_t k_begin = (int64_t)split * sk.k_per_split;
     const int64_t k_end = (k_begin + sk.k_per_split < p.k) ? k_begin + sk.k_per_split : p.k;
     const int64_t kt_count = (k_end > k_begin) ? (k_end - k_begin + BK - 1) / BK : 0;
@@ -541,10 +554,10 @@ gemm_simt_f32_8x8_kernel(const float* __restrict__ A, const float* __restrict__ 
 // How the 8 x 8 kernel would be launched for this problem: number of K splits (1 = no split)
 struct SplitPlan { int splits; int64_t k_per_split; int64_t tiles; bool use; };
 
-SplitPlan plan_8x8(const SimtParams& p, int num_sms)
+SplitPlan plan_8x8(const SimtParams& p, int num_sms, int64_t batch)
 {
     SplitPlan sp{1, 0, 0, false};
-    const int64_t tiles = ((p.m + 127) / 128) * ((p.n + 127) / 128);
+    const int64_t tiles = ((p.m + 127) / 128) * ((p.n + 127) / 128) * batch;
     sp.tiles = tiles;
     if (p.k < 16 || (p.m + 127) / 128 > 65535) return sp;
     sp.k_per_split = (p.k + 15) / 16 * 16;
@@ -562,16 +575,16 @@ SplitPlan plan_8x8(const SimtParams& p, int num_sms)
 template <typename TA, typename TB, typename TC, typename ACC>
 cudaError_t launch_typed(const GemmLaunch& g, const SimtParams& p)
 {
-    const int64_t tiles64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
+    const int64_t tiles64 = ((p.m + 63) / 64) * ((p.n + 63) / 64) * g.batch;
     if (tiles64 >= 2 * (int64_t)g.num_sms) {
         constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
-        dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)((p.m + BM - 1) / BM));
+        dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)((p.m + BM - 1) / BM), (unsigned)g.batch);
         gemm_simt_kernel<TA, TB, TC, ACC, BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, g.stream>>>(
             (const TA*)g.a, (const TB*)g.b, (TC*)g.c, g.bias, p);
     } else {
         // small problems: smaller tiles so that the grid still covers the SMs
         constexpr int BM = 32, BN = 64, BK = 16, TM = 2, TN = 4;
-        dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)((p.m + BM - 1) / BM));
+        dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)((p.m + BM - 1) / BM), (unsigned)g.batch);
         gemm_simt_kernel<TA, TB, TC, ACC, BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, g.stream>>>(
             (const TA*)g.a, (const TB*)g.b, (TC*)g.c, g.bias, p);
     }
@@ -589,13 +602,30 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err)
     p.bs0 = d.b_stride[0]; p.bs1 = d.b_stride[1];
     p.cs0 = d.c_stride[0]; p.cs1 = d.c_stride[1];
     p.alpha = d.alpha; p.beta = d.beta; p.relu = (d.epilogue == ACCB_EPI_RELU);
-    if (d.m == 0 || d.n == 0) return 0;
+    p.a_bs = g.a_batch_stride; p.b_bs = g.b_batch_stride; p.c_bs = g.c_batch_stride;
+    if (d.m == 0 || d.n == 0 || g.batch <= 0) return 0;
+    constexpr int64_t kMaxProblems = 8191;      // blockIdx.z carries problem * splits + split, splits <= 8
+    if (g.batch > kMaxProblems) {
+        auto esize = [](int t) { return (t == ACCB_F32 || t == ACCB_S32) ? 4 : (t == ACCB_F16 || t == ACCB_BF16) ? 2 : 1; };
+        int total = 0;
+        for (int64_t b0 = 0; b0 < g.batch; b0 += kMaxProblems) {
+            GemmLaunch part = g;
+            part.batch = (g.batch - b0 < kMaxProblems) ? g.batch - b0 : kMaxProblems;
+            part.a = (const char*)g.a + b0 * g.a_batch_stride * esize(d.a_type);
+            part.b = (const char*)g.b + b0 * g.b_batch_stride * esize(d.b_type);
+            part.c = (char*)g.c + b0 * g.c_batch_stride * esize(d.c_type);
+            const int n = launch_gemm_simt(part, err);
+            if (n < 0) return n;
+            total += n;
+        }
+        return total;
+    }
     if ((d.m + 31) / 32 > 65535) { *err = "SIMT GEMM: M too large for this kernel's grid"; return ACCB_ERR_ARG; }
 
     cudaError_t e;
     const int a = d.a_type, b = d.b_type, c = d.c_type;
     if (a == ACCB_F32 && b == ACCB_F32 && c == ACCB_F32) {
-        const SplitPlan sp = f32_rr_ok(g, p) ? plan_8x8(p, g.num_sms) : SplitPlan{1, 0, 0, false};
+        const SplitPlan sp = f32_rr_ok(g, p) ? plan_8x8(p, g.num_sms, g.batch) : SplitPlan{1, 0, 0, false};
         if (sp.use) {
             SplitKParams sk;
             sk.splits = sp.splits;
@@ -604,7 +634,7 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err)
             e = cudaFuncSetAttribute(gemm_simt_f32_8x8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
             if (e == cudaSuccess) {
                 cudaLaunchConfig_t cfg = {};
-                cfg.gridDim = dim3((unsigned)((p.n + 127) / 128), (unsigned)((p.m + 127) / 128), (unsigned)sp.splits);
+                cfg.gridDim = dim3((unsigned)((p.n + 127) / 128), (unsigned)((p.m + 127) / 128), (unsigned)(sp.splits * g.batch));
                 cfg.blockDim = dim3(256);
                 cfg.dynamicSmemBytes = kSmem;
                 cfg.stream = g.stream;
@@ -615,7 +645,7 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err)
                 e = cudaLaunchKernelEx(&cfg, gemm_simt_f32_8x8_kernel, (const float*)g.a, (const float*)g.b, (float*)g.c, g.bias, p, sk);
             }
         } else if (f32_rr_ok(g, p)) {
-            const int64_t tiles64 = ((p.m + 63) / 64) * ((p.n + 63) / 64);
+            const int64_t tiles64 = ((p.m + 63) / 64) * ((p.n + 63) / 64) * g.batch;
             if (tiles64 >= 2 * (int64_t)g.num_sms) e = launch_f32_rr<64, 64, 32, 4, 4, 3>(g, p);
             else e = launch_f32_rr<32, 64, 32, 2, 4, 4>(g, p);       // small problems: more, smaller tiles
         } else {

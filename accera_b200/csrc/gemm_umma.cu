@@ -49,12 +49,11 @@ namespace accb {
 namespace {
 
 constexpr int kBlockM = 128;          // accumulator rows per CTA (TMEM lanes)
-constexpr int kBlockN = 256;          // accumulator columns per tile (UMMA N)
+constexpr int kBlockN = 256;          // widest accumulator tile (UMMA N); kernels are also built for 128 columns
 constexpr int kSlabBytes = 128;       // bytes of K per stage row: one 128B swizzle atom
 constexpr int kMmaKBytes = 32;        // bytes of K one tcgen05.mma consumes
 constexpr int kThreads = 192;
 constexpr int kEpiWarps = 4;
-constexpr int kTmemCols = 512;        // two accumulators of 256 fp32 columns
 constexpr uint32_t kPeerMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address (rank 0 of a pair)
 
 enum { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2 };
@@ -62,16 +61,20 @@ enum { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2 };
 // where a bounded wait gave up (status word 1, bits 31..24)
 enum { SITE_PRODUCER_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_TMEM_EMPTY = 3, SITE_EPI_TMEM_FULL = 4 };
 
-template <bool TWO_SM> struct SmemPlan {
-    static constexpr int kABytes = kBlockM * kSlabBytes;                          // 16 KB
-    static constexpr int kBBytes = (TWO_SM ? kBlockN / 2 : kBlockN) * kSlabBytes; // 16 or 32 KB
+// BN = accumulator columns per tile: 256, or 128 for problems whose tile count fills the SMs badly at 256
+template <bool TWO_SM, int BN> struct SmemPlan {
+    static constexpr int kABytes = kBlockM * kSlabBytes;                  // 16 KB
+    static constexpr int kBBytes = (TWO_SM ? BN / 2 : BN) * kSlabBytes;   // 8 to 32 KB
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = TWO_SM ? 6 : 4;
     static constexpr int kBarrierBytes = 256;
     // epilogue staging for TMA stores: per epilogue warp two boxes of 32 rows x 128 bytes (128-byte swizzle)
     static constexpr int kStoreBoxBytes = 32 * 128;
     static constexpr int kStoreBytes = kEpiWarps * 2 * kStoreBoxBytes;
+    // as many stages as fit beside the staging boxes: 4 (1 SM, 256), 6 (pair, 256 / 1 SM, 128), 8 (pair, 128)
+    static constexpr int kBudget = 227 * 1024 - 1024 - kBarrierBytes - kStoreBytes;   // 227 KB per CTA on sm_100
+    static constexpr int kStages = kBudget / kStageBytes > 8 ? 8 : kBudget / kStageBytes;
     static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + kStoreBytes + 1024;   // +1024: manual alignment
+    static constexpr int kTmemCols = 2 * BN;   // two accumulators of BN fp32 columns (a power of two >= 32)
 };
 
 constexpr int kMaxReplicas = 8;
@@ -95,6 +98,12 @@ struct UmmaParams {
                             // (i-1)-th tiles have been loaded (or a few microseconds have passed)
     int* pace;              // this launch's progress counter
     int* status;
+    // batched GEMM: `batch` problems of the same shape in one launch; tile index = problem * tiles_m * tiles_n + tile.
+    // A batched operand has a rank-3 tensor map whose outermost coordinate is the problem; an operand shared
+    // by all problems keeps its rank-2 map.  C of problem b starts c_bs elements after that of problem b - 1.
+    int batch;
+    int a_batched, b_batched;
+    int64_t c_bs;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -182,6 +191,22 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
             "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
             ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & kPeerMask), "r"(c0), "r"(c1), "l"(pol)
             : "memory");
+}
+
+// Rank-3 forms for batched operands: the box is [1][rows][128 bytes], laid out in shared memory like the rank-2 box
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & kPeerMask), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
 }
 
 // TMA store of one shared-memory box into a C replica (rows / columns outside the tensor are clipped)
@@ -300,6 +325,18 @@ __device__ __forceinline__ void tile_coords(int t, const UmmaParams& p, int& tm,
     const int in = t - group * group_size;
     tm = first_m + in % rows;
     tn = in / rows;
+}
+
+// batched launches: tile index -> (problem, tile row, tile column)
+__device__ __forceinline__ void tile_coords_batched(int t, const UmmaParams& p, int& problem, int& tm, int& tn)
+{
+    problem = 0;
+    if (p.batch > 1) {
+        const int per = p.tiles_m * p.tiles_n;
+        problem = t / per;
+        t -= problem * per;
+    }
+    tile_coords(t, p, tm, tn);
 }
 
 // 16-byte C accesses, optionally streaming (evict-first) so that C does not displace A / B panels in L2
@@ -516,14 +553,79 @@ __device__ __forceinline__ void epilogue_to_smem(const uint32_t (&acc)[32], cons
     }
 }
 
-template <int KIND, typename TC, bool TWO_SM>
+template <int KIND> struct ElemBytes { static constexpr int value = (KIND == KIND_F16) ? 2 : (KIND == KIND_TF32) ? 4 : 1; };
+
+// One TMA box of an operand.  BATCHED launches address a batched operand through its rank-3 map (the problem is
+// the outermost coordinate, no L2 hint); an operand shared by all problems keeps the rank-2 form.
+template <bool TWO_SM, bool BATCHED>
+__device__ __forceinline__ void load_box(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                         int problem, int batched_operand, uint64_t pol)
+{
+    if (BATCHED && batched_operand) {
+        if constexpr (TWO_SM) tma_load_3d_pair(dst, map, bar, c0, c1, problem);
+        else tma_load_3d(dst, map, bar, c0, c1, problem);
+    } else {
+        if constexpr (TWO_SM) tma_load_2d_pair(dst, map, bar, c0, c1, pol);
+        else tma_load_2d(dst, map, bar, c0, c1, pol);
+    }
+}
+
+// Loads k-block `kb` of this CTA's A rows and B rows into one pipeline stage.  The operand layouts are template
+// parameters so that every box count, offset and coordinate step below is a compile-time constant.
+//   K-major operand:  one box [rows][128 B of K]
+//   MN-major operand: one box [k rows][128 B of M / N] per 128-byte block of the tile's M / N extent, stacked
+template <int KIND, bool TWO_SM, int BN, bool A_MN, bool B_MN, bool BATCHED>
+__device__ __forceinline__ void load_stage(const CUtensorMap* map_a, const CUtensorMap* map_b, uint32_t sa, uint32_t sb,
+                                           uint32_t bar, int kb, int row_a, int row_b, int problem, int a_batched,
+                                           int b_batched, uint64_t pol_a, uint64_t pol_b)
+{
+    constexpr int SE = kSlabBytes / ElemBytes<KIND>::value;      // elements in 128 bytes
+    constexpr int kRowsB = TWO_SM ? BN / 2 : BN;
+    constexpr uint32_t kBoxBytes = (uint32_t)(kSlabBytes * SE);  // one MN-major box
+    if constexpr (!A_MN) {
+        load_box<TWO_SM, BATCHED>(sa, map_a, bar, kb * SE, row_a, problem, a_batched, pol_a);
+    } else {
+#pragma unroll
+        for (int blk = 0; blk < kBlockM / SE; ++blk)
+            load_box<TWO_SM, BATCHED>(sa + blk * kBoxBytes, map_a, bar, row_a + blk * SE, kb * SE, problem, a_batched, pol_a);
+    }
+    if constexpr (!B_MN) {
+        load_box<TWO_SM, BATCHED>(sb, map_b, bar, kb * SE, row_b, problem, b_batched, pol_b);
+    } else {
+        static_assert(kRowsB % SE == 0 || !B_MN, "an MN-major B box is 128 bytes of N wide");
+#pragma unroll
+        for (int blk = 0; blk < kRowsB / SE; ++blk)
+            load_box<TWO_SM, BATCHED>(sb + blk * kBoxBytes, map_b, bar, row_b + blk * SE, kb * SE, problem, b_batched, pol_b);
+    }
+}
+
+// Issues the tcgen05.mma instructions that consume one stage (128 bytes of K per row).
+//   K-major operand:  advancing K inside the swizzle atom is +32 bytes on the descriptor's start address
+//   MN-major operand: one MMA consumes (32 / element bytes) k-rows of 128 bytes each
+template <int KIND, bool TWO_SM, bool A_MN, bool B_MN>
+__device__ __forceinline__ void issue_stage(uint32_t tmem_d, uint32_t sa, uint32_t sb, uint32_t idesc, bool first_kb)
+{
+    constexpr int EB = ElemBytes<KIND>::value;
+    constexpr uint32_t kBoxBytes = (uint32_t)(kSlabBytes * (kSlabBytes / EB));
+    constexpr uint64_t kStepMn = (uint64_t)(((kMmaKBytes / EB) * kSlabBytes) >> 4);
+    constexpr uint64_t kStepK = (uint64_t)(kMmaKBytes >> 4);
+    const uint64_t adesc = A_MN ? make_smem_desc_mn(sa, kBoxBytes) : make_smem_desc(sa);
+    const uint64_t bdesc = B_MN ? make_smem_desc_mn(sb, kBoxBytes) : make_smem_desc(sb);
+#pragma unroll
+    for (int j = 0; j < kSlabBytes / kMmaKBytes; ++j)
+        umma<KIND, TWO_SM>(tmem_d, adesc + (uint64_t)j * (A_MN ? kStepMn : kStepK), bdesc + (uint64_t)j * (B_MN ? kStepMn : kStepK),
+                           idesc, (!first_kb || j > 0) ? 1u : 0u);
+}
+
+template <int KIND, typename TC, bool TWO_SM, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CReplicaMaps cmaps, TC* __restrict__ C, const float* __restrict__ bias,
                  const UmmaParams p)
 {
-    using Plan = SmemPlan<TWO_SM>;
+    using Plan = SmemPlan<TWO_SM, BN>;
     using ACC = typename std::conditional<KIND == KIND_I8, int, float>::type;
+    constexpr int kTmemCols = Plan::kTmemCols;
     constexpr int S = Plan::kStages;
     constexpr int kCtas = TWO_SM ? 2 : 1;
 
@@ -571,14 +673,17 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_holder;
 
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
     const int num_units = (int)gridDim.x / kCtas;
     const int unit = (int)blockIdx.x / kCtas;
-    const int slab_elems = kSlabBytes / p.elem_bytes;
+    constexpr int slab_elems = kSlabBytes / ElemBytes<KIND>::value;
     const int num_kb = (int)((p.k + slab_elems - 1) / slab_elems);
-    const bool k_major_both = !p.a_mn && !p.b_mn;
-    const uint32_t mn_block = (uint32_t)(kSlabBytes * slab_elems);                      // bytes of one MN-major box
-    const uint32_t mn_step = (uint32_t)((kMmaKBytes / p.elem_bytes) * kSlabBytes);      // bytes one MMA advances in it
+    // operand layouts (bit 0: A is MN-major, bit 1: B is MN-major) and batching select one of the
+    // compile-time specialised stage routines; the choice is uniform over the launch
+    const int layout = (p.a_mn ? 1 : 0) | (p.b_mn ? 2 : 0);
+    // an MN-major B box is 128 bytes of N: a CTA's share of B must be at least that wide (not so for 8-bit
+    // operands in a 128-column pair tile; the host never selects that combination)
+    constexpr bool kBMnOk = ((TWO_SM ? BN / 2 : BN) % slab_elems) == 0;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -589,10 +694,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             int tile_i = 0;
             bool pacing = (p.pace_pct > 0) && leader;
             for (int t = unit; t < num_tiles && ok; t += num_units, ++tile_i) {
-                int tm, tn;
-                tile_coords(t, p, tm, tn);
+                int problem, tm, tn;
+                tile_coords_batched(t, p, problem, tm, tn);
                 const int row_a = (tm * kCtas + (int)rank) * kBlockM;
-                const int row_b = tn * kBlockN + (TWO_SM ? (int)rank * (kBlockN / 2) : 0);
+                const int row_b = tn * BN + (TWO_SM ? (int)rank * (BN / 2) : 0);
                 if (pacing && tile_i > 0) {
                     // Pacing, not a dependency: CTAs that drift apart stop finding each other's A / B panels in
                     // L2 (they are re-read from DRAM instead).  Wait, for at most ~20 us, until most CTAs have
@@ -614,36 +719,26 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     } else {
                         mbar_arrive_expect_tx(full_bar(s), (uint32_t)Plan::kStageBytes);
                     }
-                    if (k_major_both) {
-                        // both operands K-contiguous: one box [rows][128 B of K] each
-                        if constexpr (TWO_SM) {
-                            tma_load_2d_pair(sa, &map_a, full_bar(s), kb * slab_elems, row_a, pol_a);
-                            tma_load_2d_pair(sb, &map_b, full_bar(s), kb * slab_elems, row_b, pol_b);
-                        } else {
-                            tma_load_2d(sa, &map_a, full_bar(s), kb * slab_elems, row_a, pol_a);
-                            tma_load_2d(sb, &map_b, full_bar(s), kb * slab_elems, row_b, pol_b);
+                    const uint32_t fb = full_bar(s);
+#define ACCB_LOAD_STAGE(AMN, BMN, BATCHED)                                                                        \
+    load_stage<KIND, TWO_SM, BN, AMN, BMN, BATCHED>(&map_a, &map_b, sa, sb, fb, kb, row_a, row_b, problem, p.a_batched, \
+                                                    p.b_batched, pol_a, pol_b)
+                    if (p.batch == 1) {
+                        if (layout == 0) ACCB_LOAD_STAGE(false, false, false);
+                        else if (layout == 1) ACCB_LOAD_STAGE(true, false, false);
+                        else if constexpr (kBMnOk) {
+                            if (layout == 2) ACCB_LOAD_STAGE(false, true, false);
+                            else ACCB_LOAD_STAGE(true, true, false);
                         }
                     } else {
-                        auto load = [&](uint32_t dst, const CUtensorMap* map, int c0, int c1, uint64_t pol) {
-                            if constexpr (TWO_SM) tma_load_2d_pair(dst, map, full_bar(s), c0, c1, pol);
-                            else tma_load_2d(dst, map, full_bar(s), c0, c1, pol);
-                        };
-                        // MN-major operand: one box [k rows][128 B of MN] per 128-byte block of the tile's MN
-                        // extent, stacked in shared memory
-                        if (!p.a_mn) {
-                            load(sa, &map_a, kb * slab_elems, row_a, pol_a);
-                        } else {
-                            for (int blk = 0; blk < kBlockM / slab_elems; ++blk)
-                                load(sa + blk * (kSlabBytes * slab_elems), &map_a, row_a + blk * slab_elems, kb * slab_elems, pol_a);
-                        }
-                        constexpr int kRowsB = TWO_SM ? kBlockN / 2 : kBlockN;
-                        if (!p.b_mn) {
-                            load(sb, &map_b, kb * slab_elems, row_b, pol_b);
-                        } else {
-                            for (int blk = 0; blk < kRowsB / slab_elems; ++blk)
-                                load(sb + blk * (kSlabBytes * slab_elems), &map_b, row_b + blk * slab_elems, kb * slab_elems, pol_b);
+                        if (layout == 0) ACCB_LOAD_STAGE(false, false, true);
+                        else if (layout == 1) ACCB_LOAD_STAGE(true, false, true);
+                        else if constexpr (kBMnOk) {
+                            if (layout == 2) ACCB_LOAD_STAGE(false, true, true);
+                            else ACCB_LOAD_STAGE(true, true, true);
                         }
                     }
+#undef ACCB_LOAD_STAGE
                 }
                 if (p.pace_pct > 0 && leader && ok) atomicAdd(p.pace, 1);   // counted even after this CTA stopped waiting
             }
@@ -659,7 +754,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const uint32_t tph = (local >> 1) & 1u;
                 if (!mbar_wait(tmem_empty_bar(buf), tph ^ 1u, p.status, SITE_MMA_TMEM_EMPTY, local)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kBlockN);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % S;
                     const uint32_t ph = (it / S) & 1u;
@@ -667,28 +762,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t sa = smem_base + s * Plan::kStageBytes;
                     const uint32_t sb = sa + Plan::kABytes;
-                    if (k_major_both) {
-                        // advancing K inside the swizzle atom: +32 bytes on the start address (16-byte units)
-                        const uint64_t adesc = make_smem_desc(sa);
-                        const uint64_t bdesc = make_smem_desc(sb);
-#pragma unroll
-                        for (int j = 0; j < kSlabBytes / kMmaKBytes; ++j) {
-                            umma<KIND, TWO_SM>(tmem_d, adesc + (uint64_t)(j * (kMmaKBytes >> 4)),
-                                               bdesc + (uint64_t)(j * (kMmaKBytes >> 4)), p.idesc,
-                                               (kb > 0 || j > 0) ? 1u : 0u);
-                        }
-                    } else {
-                        // MN-major operand: one MMA consumes (32 / elem_bytes) k-rows of 128 bytes each
-                        const uint64_t adesc = p.a_mn ? make_smem_desc_mn(sa, mn_block) : make_smem_desc(sa);
-                        const uint64_t bdesc = p.b_mn ? make_smem_desc_mn(sb, mn_block) : make_smem_desc(sb);
-                        const uint64_t astep = (uint64_t)((p.a_mn ? mn_step : (uint32_t)kMmaKBytes) >> 4);
-                        const uint64_t bstep = (uint64_t)((p.b_mn ? mn_step : (uint32_t)kMmaKBytes) >> 4);
-#pragma unroll
-                        for (int j = 0; j < kSlabBytes / kMmaKBytes; ++j) {
-                            umma<KIND, TWO_SM>(tmem_d, adesc + (uint64_t)j * astep, bdesc + (uint64_t)j * bstep, p.idesc,
-                                               (kb > 0 || j > 0) ? 1u : 0u);
-                        }
-                    }
+                    if (layout == 0) issue_stage<KIND, TWO_SM, false, false>(tmem_d, sa, sb, p.idesc, kb == 0);
+                    else if (layout == 1) issue_stage<KIND, TWO_SM, true, false>(tmem_d, sa, sb, p.idesc, kb == 0);
+                    else if (layout == 2) issue_stage<KIND, TWO_SM, false, true>(tmem_d, sa, sb, p.idesc, kb == 0);
+                    else issue_stage<KIND, TWO_SM, true, true>(tmem_d, sa, sb, p.idesc, kb == 0);
                     umma_commit<TWO_SM>(empty_bar(s));            // frees the stage once these MMAs have read it
                 }
                 if (ok) umma_commit<TWO_SM>(tmem_full_bar(buf));  // accumulator complete
@@ -698,26 +775,26 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ---------------- epilogue warps ----------------
         const int q = warp & 3;                       // TMEM lane quarter this warp may access
         const bool c_vec = (p.cs1 == 1) && ((p.cs0 * (int64_t)sizeof(TC)) % 16 == 0) &&
-                           ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+                           ((p.c_bs * (int64_t)sizeof(TC)) % 16 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
         int local = 0;
         bool ok = true;
         uint32_t store_count = 0;                    // TMA-store boxes this warp has issued (warp-uniform)
         uint8_t* store_stage = smem_gen + S * Plan::kStageBytes + (size_t)(warp - 2) * 2 * Plan::kStoreBoxBytes;
         for (int t = unit; t < num_tiles && ok; t += num_units, ++local) {
-            int tm, tn;
-            tile_coords(t, p, tm, tn);
+            int problem, tm, tn;
+            tile_coords_batched(t, p, problem, tm, tn);
             const int buf = local & 1;
             const uint32_t tph = (local >> 1) & 1u;
             // all 32 lanes must agree before the warp-wide TMEM loads below
             if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), tph, p.status, SITE_EPI_TMEM_FULL, local))) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int64_t row = (int64_t)(tm * kCtas + (int)rank) * kBlockM + q * 32 + lane;
-            const int64_t col_tile = (int64_t)tn * kBlockN;
-            TC* crow = C + row * p.cs0;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kBlockN);
+            const int64_t col_tile = (int64_t)tn * BN;
+            TC* crow = C + (int64_t)problem * p.c_bs + row * p.cs0;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             const int64_t row0 = (int64_t)(tm * kCtas + (int)rank) * kBlockM + q * 32;     // first row of this warp
 #pragma unroll 1
-            for (int c = 0; c < kBlockN / 32; ++c) {
+            for (int c = 0; c < BN / 32; ++c) {
                 uint32_t acc[32];
                 tmem_ld32(taddr + (uint32_t)(c * 32), acc);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -817,7 +894,7 @@ int elem_size(int t)
 
 // K-major operand [rows, k] with `ld` elements between rows; box = 128 bytes of K by box_rows rows
 bool make_operand_map(CUtensorMap* map, const void* base, int type, int64_t rows, int64_t k, int64_t ld, int box_rows,
-                      bool mn_major = false)
+                      bool mn_major = false, int64_t batch = 1, int64_t batch_stride = 0)
 {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return false;
@@ -831,11 +908,14 @@ bool make_operand_map(CUtensorMap* map, const void* base, int type, int64_t rows
     const int es = elem_size(type);
     // K-major: [rows][k], k contiguous, box = 128 bytes of k by box_rows rows.
     // MN-major: the array is [k][rows] with `rows` (M or N) contiguous; box = 128 bytes of M/N by (128 / es) k-rows.
-    cuuint64_t dims[2] = { (cuuint64_t)(mn_major ? rows : k), (cuuint64_t)(mn_major ? k : rows) };
-    cuuint64_t strides[1] = { (cuuint64_t)(ld * es) };
-    cuuint32_t box[2] = { (cuuint32_t)(kSlabBytes / es), (cuuint32_t)(mn_major ? kSlabBytes / es : box_rows) };
-    cuuint32_t estr[2] = { 1, 1 };
-    CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    // Batched (batch > 1 with a non-zero batch stride): a third, outermost dimension walks the problems; the box
+    // is one problem thick, so it lands in shared memory exactly like the rank-2 box.
+    const bool rank3 = batch > 1 && batch_stride > 0;
+    cuuint64_t dims[3] = { (cuuint64_t)(mn_major ? rows : k), (cuuint64_t)(mn_major ? k : rows), (cuuint64_t)batch };
+    cuuint64_t strides[2] = { (cuuint64_t)(ld * es), (cuuint64_t)(batch_stride * es) };
+    cuuint32_t box[3] = { (cuuint32_t)(kSlabBytes / es), (cuuint32_t)(mn_major ? kSlabBytes / es : box_rows), 1 };
+    cuuint32_t estr[3] = { 1, 1, 1 };
+    CUresult r = enc(map, dt, rank3 ? 3 : 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
@@ -888,41 +968,93 @@ uint32_t make_idesc(int a_type, int b_type, bool int_acc, bool f16_out_acc, int 
     return d;
 }
 
-template <int KIND, typename TC, bool TWO_SM>
+template <int KIND, typename TC, bool TWO_SM, int BN>
 int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap& mb, const CReplicaMaps& cm, UmmaParams p,
                    const char** err)
 {
-    using Plan = SmemPlan<TWO_SM>;
-    auto kernel = gemm_umma_kernel<KIND, TC, TWO_SM>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal);
-    if (e != cudaSuccess) { *err = cudaGetErrorString(e); return ACCB_ERR_CUDA; }
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    using Plan = SmemPlan<TWO_SM, BN>;
+    auto kernel = gemm_umma_kernel<KIND, TC, TWO_SM, BN>;
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = Plan::kTotal;
     cfg.stream = g.stream;
     cudaLaunchAttribute attr[1];
-    int units = g.num_sms;
     if (TWO_SM) {
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr; cfg.numAttrs = 1;
-        cfg.gridDim = dim3(2 * (unsigned)(g.num_sms / 2));
-        int max_clusters = 0;
-        e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
-        if (e != cudaSuccess || max_clusters < 1) { *err = "tcgen05 GEMM: no CTA pair can be resident"; (void)cudaGetLastError(); return ACCB_ERR_CUDA; }
-        units = max_clusters < g.num_sms / 2 ? max_clusters : g.num_sms / 2;
     }
+    // Per device and kernel variant, once: opt in to the large dynamic shared memory and find how many CTAs
+    // (pairs) can be resident.  Both calls cost microseconds, which is the whole run time of a small GEMM.
+    constexpr int kMaxDevices = 64;
+    static std::atomic<int> resident_units[kMaxDevices];
+    const int slot = (g.device >= 0 && g.device < kMaxDevices) ? g.device : -1;
+    int units = slot >= 0 ? resident_units[slot].load(std::memory_order_acquire) : 0;
+    if (units == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal);
+        if (e != cudaSuccess) { *err = cudaGetErrorString(e); return ACCB_ERR_CUDA; }
+        units = g.num_sms;
+        if (TWO_SM) {
+            cfg.gridDim = dim3(2 * (unsigned)(g.num_sms / 2));
+            int max_clusters = 0;
+            e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
+            if (e != cudaSuccess || max_clusters < 1) { *err = "tcgen05 GEMM: no CTA pair can be resident"; (void)cudaGetLastError(); return ACCB_ERR_CUDA; }
+            units = max_clusters < g.num_sms / 2 ? max_clusters : g.num_sms / 2;
+        }
+        if (slot >= 0) resident_units[slot].store(units, std::memory_order_release);
+    }
+    const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
     if (g.d.max_ctas > 0) {
         const int cap = g.d.max_ctas / (TWO_SM ? 2 : 1);
         if (cap >= 1 && cap < units) units = cap;
     }
     if (units > num_tiles) units = num_tiles;
     cfg.gridDim = dim3((unsigned)(units * (TWO_SM ? 2 : 1)));
-    e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, cm, (TC*)g.c, g.bias, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, cm, (TC*)g.c, g.bias, p);
     if (e != cudaSuccess) { *err = cudaGetErrorString(e); return ACCB_ERR_CUDA; }
     note_launches(1);
     return 1;
+}
+
+// Tile shape for one problem: CTA pairs (256-row tiles) or single CTAs (128 rows), 256 or 128 columns.
+// The kernel is persistent, so its run time is (rounds of tiles) x (time of one tile) plus the last tile's
+// epilogue, which nothing overlaps.  A wide pair tile is the most efficient per flop, but a problem whose
+// tile count is just over a multiple of the resident CTAs wastes most of a round; a narrower tile then wins.
+struct TileChoice { bool two_sm; int bn; };
+
+TileChoice choose_tile(const GemmLaunch& g, int want_two_sm /* -1: free, 0 / 1: fixed by the caller */)
+{
+    const accb_gemm_desc& d = g.d;
+    const int64_t batch = g.batch > 1 ? g.batch : 1;
+    const bool b_mn = d.b_stride[0] != 1;
+    const bool eight_bit = elem_size(d.a_type) == 1;
+    // throughput of each tile shape on a large square bf16 problem relative to the 256-column pair tile (measured:
+    // 1518 / 1346 / 972 / 851 TFLOP/s at 8192^3).  128-column tiles need 1.5x the L2 -> shared-memory traffic
+    // per flop and are bound by it; they only pay on problems too small to give every SM a 256-column tile.
+    static const double kEff[2][2] = { /* 1 SM */ { 0.64 /*128*/, 0.89 /*256*/ }, /* pair */ { 0.56 /*128*/, 1.00 /*256*/ } };
+    int force_bn = 0;
+    if (const char* tune = getenv("ACCB_GEMM_TUNE"))
+        for (const char* q = tune; *q; ++q)
+            if (q[0] == 'n' && q[1] == '=') force_bn = atoi(q + 2);
+    TileChoice best{want_two_sm != 0, kBlockN};
+    double best_cost = -1.0;
+    for (int two = 1; two >= 0; --two) {
+        if (want_two_sm >= 0 && two != want_two_sm) continue;
+        for (int bn = 256; bn >= 128; bn -= 128) {
+            if (force_bn && bn != force_bn) continue;
+            if (two && bn == 128 && eight_bit && b_mn) continue;      // a 64-column share of B is narrower than one box
+            const int64_t rows = two ? 2 * kBlockM : kBlockM;
+            const int64_t tiles = ((d.m + rows - 1) / rows) * ((d.n + bn - 1) / bn) * batch;
+            int64_t units = two ? g.num_sms / 2 : g.num_sms;
+            if (d.max_ctas > 0 && d.max_ctas / (two ? 2 : 1) >= 1 && d.max_ctas / (two ? 2 : 1) < units) units = d.max_ctas / (two ? 2 : 1);
+            const int64_t rounds = (tiles + units - 1) / units;
+            const double k_steps = (double)((d.k + 63) / 64);
+            // per tile: K loop + (only for the last round) the epilogue, both proportional to the tile's columns
+            const double cost = ((double)rounds * k_steps + 6.0) * bn / kEff[two][bn == 256];
+            if (best_cost < 0.0 || cost < best_cost * 0.97) { best_cost = cost; best = TileChoice{two != 0, bn}; }
+        }
+    }
+    return best;
 }
 
 }  // namespace
@@ -949,23 +1081,33 @@ bool gemm_umma_supported(const GemmLaunch& g, const char** why)
     const int64_t pitch_a = a_k ? d.a_stride[0] : d.a_stride[1], pitch_b = b_k ? d.b_stride[1] : d.b_stride[0];
     if ((pitch_a * es) % 16 || (pitch_b * es) % 16) { *why = "operand row pitch must be a multiple of 16 bytes"; return false; }
     if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15)) { *why = "operand base must be 16-byte aligned"; return false; }
+    if (g.batch > 1) {
+        if (g.n_extra_c > 0) { *why = "C replicas are not available for batched GEMMs"; return false; }
+        if (g.a_batch_stride < 0 || g.b_batch_stride < 0 || g.c_batch_stride < 0) { *why = "batch strides must not be negative"; return false; }
+        if ((g.a_batch_stride * es) % 16 || (g.b_batch_stride * es) % 16) { *why = "operand batch stride must be a multiple of 16 bytes"; return false; }
+        if (g.batch > (1 << 20)) { *why = "too many problems in one batched call"; return false; }
+    }
     if (d.m < 1 || d.n < 1 || d.k < 1) { *why = "empty problem"; return false; }
     if (d.m > (int64_t)1 << 30 || d.n > (int64_t)1 << 30 || d.k > (int64_t)1 << 30) { *why = "dimension too large"; return false; }
     if (!encode_tiled_fn()) { *why = "cuTensorMapEncodeTiled is not available"; return false; }
     return true;
 }
 
-int launch_gemm_umma(const GemmLaunch& g, bool two_sm, const char** err)
+int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
 {
     const accb_gemm_desc& d = g.d;
     const char* why = nullptr;
     if (!gemm_umma_supported(g, &why)) { *err = why; return ACCB_ERR_ARG; }
 
+    const TileChoice tile = choose_tile(g, want_two_sm);
+    const bool two_sm = tile.two_sm;
+    const int bn = tile.bn;
     CUtensorMap ma, mb;
-    const int b_box_rows = two_sm ? kBlockN / 2 : kBlockN;
+    const int b_box_rows = two_sm ? bn / 2 : bn;
     const bool a_mn = d.a_stride[1] != 1, b_mn = d.b_stride[0] != 1;
-    if (!make_operand_map(&ma, g.a, d.a_type, d.m, d.k, a_mn ? d.a_stride[1] : d.a_stride[0], kBlockM, a_mn) ||
-        !make_operand_map(&mb, g.b, d.b_type, d.n, d.k, b_mn ? d.b_stride[0] : d.b_stride[1], b_box_rows, b_mn)) {
+    const int64_t batch = g.batch > 1 ? g.batch : 1;
+    if (!make_operand_map(&ma, g.a, d.a_type, d.m, d.k, a_mn ? d.a_stride[1] : d.a_stride[0], kBlockM, a_mn, batch, g.a_batch_stride) ||
+        !make_operand_map(&mb, g.b, d.b_type, d.n, d.k, b_mn ? d.b_stride[0] : d.b_stride[1], b_box_rows, b_mn, batch, g.b_batch_stride)) {
         *err = "tcgen05 GEMM: cuTensorMapEncodeTiled failed";
         return ACCB_ERR_CUDA;
     }
@@ -975,17 +1117,21 @@ int launch_gemm_umma(const GemmLaunch& g, bool two_sm, const char** err)
     p.m = d.m; p.n = d.n; p.k = d.k;
     p.cs0 = d.c_stride[0]; p.cs1 = d.c_stride[1];
     p.alpha = d.alpha; p.beta = d.beta; p.relu = (d.epilogue == ACCB_EPI_RELU);
-    p.idesc = make_idesc(d.a_type, d.b_type, int_acc, false, two_sm ? 2 * kBlockM : kBlockM, kBlockN, a_mn, b_mn);
+    p.idesc = make_idesc(d.a_type, d.b_type, int_acc, false, two_sm ? 2 * kBlockM : kBlockM, bn, a_mn, b_mn);
     p.a_mn = a_mn; p.b_mn = b_mn;
     p.elem_bytes = elem_size(d.a_type);
     const int rows_per_unit = two_sm ? 2 * kBlockM : kBlockM;
     p.tiles_m = (int)((d.m + rows_per_unit - 1) / rows_per_unit);
-    p.tiles_n = (int)((d.n + kBlockN - 1) / kBlockN);
+    p.tiles_n = (int)((d.n + bn - 1) / bn);
     p.group_m = two_sm ? 8 : 16;
-    const int64_t tiles_total = (int64_t)p.tiles_m * p.tiles_n;
+    p.batch = (int)batch;
+    p.a_batched = (batch > 1 && g.a_batch_stride > 0) ? 1 : 0;
+    p.b_batched = (batch > 1 && g.b_batch_stride > 0) ? 1 : 0;
+    p.c_bs = batch > 1 ? g.c_batch_stride : 0;
+    const int64_t tiles_total = (int64_t)p.tiles_m * p.tiles_n * batch;
     const int64_t units_est = two_sm ? g.num_sms / 2 : g.num_sms;
     p.hint_a = 0; p.hint_b = 0; p.c_stream = 0;
-    p.tma_store = c_tma_storable(d, g.c) ? 1 : 0;
+    p.tma_store = (c_tma_storable(d, g.c) && batch == 1) ? 1 : 0;   // batched: C is written with plain stores
     p.n_replicas = 1 + g.n_extra_c;
     // Long launches: keep the persistent CTAs in step tile by tile.  Left alone they drift apart over a hundred
     // rounds of tiles and stop sharing A / B panels in L2 (measured on 65536 x 8192 x 8192: 22.8 GB of DRAM
@@ -1025,10 +1171,13 @@ int launch_gemm_umma(const GemmLaunch& g, bool two_sm, const char** err)
         if (!ok) { *err = "tcgen05 GEMM: cuTensorMapEncodeTiled failed for C"; return ACCB_ERR_CUDA; }
     }
     p.status = g.status;
-    if ((int64_t)p.tiles_m * p.tiles_n > 0x3fffffff) { *err = "tcgen05 GEMM: too many tiles"; return ACCB_ERR_ARG; }
+    if (tiles_total > 0x3fffffff) { *err = "tcgen05 GEMM: too many tiles"; return ACCB_ERR_ARG; }
 
-#define ACCB_UMMA_LAUNCH(KIND, TC)                                                          \
-    (two_sm ? launch_variant<KIND, TC, true>(g, ma, mb, cm, p, err) : launch_variant<KIND, TC, false>(g, ma, mb, cm, p, err))
+#define ACCB_UMMA_LAUNCH(KIND, TC)                                                                          \
+    (two_sm ? (bn == 256 ? launch_variant<KIND, TC, true, 256>(g, ma, mb, cm, p, err)                       \
+                         : launch_variant<KIND, TC, true, 128>(g, ma, mb, cm, p, err))                      \
+            : (bn == 256 ? launch_variant<KIND, TC, false, 256>(g, ma, mb, cm, p, err)                      \
+                         : launch_variant<KIND, TC, false, 128>(g, ma, mb, cm, p, err)))
 
     if (d.a_type == ACCB_F16 || d.a_type == ACCB_BF16) {
         if (d.c_type == ACCB_F32) return ACCB_UMMA_LAUNCH(KIND_F16, float);

@@ -104,6 +104,20 @@ class MMAShape(enum.Enum):
     M16xN16xK8_B1 = 10
 
 
+class _TensorCoreInfo:
+    """Shape arithmetic the reference's GPU tests use to size their tiles before tensorizing
+    (Targets.py:770-793).  The shapes are read off the MMAShape member's name."""
+
+    @staticmethod
+    def mma_shape_to_tuple(mma_shape: MMAShape) -> Tuple[int, int, int]:
+        m, n, k = mma_shape.name.split("_")[0].split("x")
+        return int(m[1:]), int(n[1:]), int(k[1:])
+
+    def compute_tensor_splits(self, mma_shape: MMAShape, num_total_passes: int = 1) -> Tuple[int, int, int]:
+        m, n, k = self.mma_shape_to_tuple(mma_shape)
+        return m, n, k * int(num_total_passes)
+
+
 class MMASchedulingPolicy(enum.Enum):
     PASS_ORDER = 0
     BLOCK_ORDER = 1
@@ -180,6 +194,7 @@ class Target:
         self.category = category or (Target.Category.CPU if known_name is Target.Model.HOST else Target.Category.GPU)
         self.runtime = "CUDA" if self.category is Target.Category.GPU else "NONE"
         self.extra = dict(kwargs)
+        self.tensor_core_info = _TensorCoreInfo()
 
     def is_compatible_with(self, other: "Target") -> bool:
         return self.category == other.category and self.runtime == other.runtime
@@ -535,8 +550,19 @@ class Schedule:
     def pad(self, index, size):
         self.transformations.append(("pad", (index, size)))
 
-    def create_plan(self, target: Optional[Target] = None) -> "Plan":
+    def create_plan(self, target: Optional[Target] = None, **_ignored) -> "Plan":
         return Plan(self, target or Target.HOST)
+
+    def _create_tensorizable_plan(self, target, block_indices, warp_indices, tensor_indices, outer_nest_order,
+                                  dynamic_shared_memory_size: int = 0, blocks_per_SM: int = 0):
+        """Helper of the reference's GPU tests (lang/Schedule.py:499-519): puts the three tensor indices
+        innermost, binds block and warp indices to the grid and returns (plan, tensor_indices)."""
+        self.reorder(*outer_nest_order, *tensor_indices)
+        plan = self.create_plan(target=target)
+        (i, j), (ii, jj) = block_indices, warp_indices
+        units = Target.GridUnit
+        plan.bind(mapping={i: units.BLOCK_Y, j: units.BLOCK_X, ii: units.WARP_Y, jj: units.WARP_X})
+        return plan, tensor_indices
 
 
 def fuse(*args, partial: Optional[int] = None) -> Schedule:

@@ -22,7 +22,7 @@ import secrets
 import shutil
 import subprocess
 from collections import OrderedDict
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 from . import lang, patterns
 from .hat import hat_file
@@ -133,6 +133,8 @@ class Package:
                         raise ValueError(f"dimension {s!r} sizes {arr!r} but is missing from args")
         if spec.kind == "gemm":
             need(spec.a, spec.b, spec.c, spec.bias)
+            if spec.batch is not None and (spec.a.is_dynamic or spec.b.is_dynamic or spec.c.is_dynamic):
+                raise patterns.UnsupportedNestError("batch matmul is implemented for statically shaped arrays")
             if spec.c.role is not Role.INPUT_OUTPUT and spec.c.role is not Role.OUTPUT:
                 raise ValueError("the GEMM result array must be INPUT_OUTPUT")
             key = (spec.a.element_type, spec.b.element_type, spec.c.element_type)
@@ -362,8 +364,20 @@ class Package:
 
         body: List[str] = []
         s = fn.spec
-        if s.kind == "gemm":
+        batched = s.kind == "gemm" and s.batch is not None
+        if batched:
+            def split(arr: Array, pos) -> Tuple[List[str], str]:
+                st = arr.strides()
+                return ([f"INT64_C({st[pos[1]]})", f"INT64_C({st[pos[2]]})"],
+                        f"INT64_C({st[pos[0]] if pos[0] is not None else 0})")
+            (sa, a_bs), (sb, b_bs), (sc, c_bs) = split(s.a, s.a_pos), split(s.b, s.b_pos), split(s.c, s.c_pos)
+            call = (f"accb_gemm_batched(&d, {dim(s.batch)}, {a_bs}, {b_bs}, {c_bs}, {arg_name[id(s.a)]}, "
+                    f"{arg_name[id(s.b)]}, {arg_name[id(s.c)]}, nullptr)")
+        elif s.kind == "gemm":
             sa, sb, sc = strides(s.a, s.a_transposed), strides(s.b, s.b_transposed), strides(s.c)
+            call = (f"accb_gemm(&d, {arg_name[id(s.a)]}, {arg_name[id(s.b)]}, {arg_name[id(s.c)]}, "
+                    f"{arg_name[id(s.bias)] if s.bias is not None else 'nullptr'})")
+        if s.kind == "gemm":
             body += [
                 "    accb_gemm_desc d = {};",
                 f"    d.m = {dim(s.m)}; d.n = {dim(s.n)}; d.k = {dim(s.k)};",
@@ -375,8 +389,7 @@ class Package:
                 f"    d.c_stride[0] = {sc[0]}; d.c_stride[1] = {sc[1]};",
                 f"    d.alpha = {float(s.alpha)!r}f; d.beta = {float(s.beta)!r}f;",
                 f"    d.epilogue = {'ACCB_EPI_RELU' if s.relu else 'ACCB_EPI_NONE'};",
-                f"    report(\"{fn.name}\", accb_gemm(&d, {arg_name[id(s.a)]}, {arg_name[id(s.b)]}, {arg_name[id(s.c)]}, "
-                f"{arg_name[id(s.bias)] if s.bias is not None else 'nullptr'}));",
+                f"    report(\"{fn.name}\", {call});",
             ]
         elif s.kind == "reduce_mean":
             shape = list(s.data.shape)

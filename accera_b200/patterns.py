@@ -8,6 +8,8 @@ of each form in parentheses):
   matmul          C[i,j] += A[i,k] * B[k,j]           (README.md:61-65; operands may be accessed
                                                        transposed, int_matmul_tests.py:55 uses B[j,k];
                                                        casts around operands or the product are allowed)
+  batch matmul    C[b,i,j] += A[b,i,k] * B[b,k,j]      (mfma_tests.py:435-466; any index order inside an
+                                                       access; an operand without b is shared by the batch)
   + bias          C[i,j] += bias[j]                    (new: the reference has no bias epilogue)
   + relu          C[i,j] = max(C[i,j], 0)              (README.md:67-76), fused with partial=2, or
                                                        MMAFragmentOp.ReLU as tensorize epilogue
@@ -47,6 +49,12 @@ class GemmSpec:
     beta: float = 1.0
     compute: str = "auto"      # "auto" | "simt" | "tensor"
     kind: str = "gemm"
+    # batch matmul only: number of problems, and per array the positions of its (batch, row, column)
+    # indices among the array's dimensions (batch position None = the operand is shared by all problems)
+    batch: Any = None
+    a_pos: Optional[Tuple[Optional[int], int, int]] = None
+    b_pos: Optional[Tuple[Optional[int], int, int]] = None
+    c_pos: Optional[Tuple[Optional[int], int, int]] = None
 
 
 @dataclasses.dataclass
@@ -124,6 +132,58 @@ def _match_matmul(nest: Nest) -> Optional[GemmSpec]:
                     a_transposed=a_acc.indices[0] is k, b_transposed=b_acc.indices[0] is j)
 
 
+def _match_batch_matmul(nest: Nest) -> Optional[GemmSpec]:
+    if len(nest.shape) != 4 or len(nest.statements) != 1:
+        return None
+    s = nest.statements[0]
+    if s.kind != "assign" or s.op != "+":
+        return None
+    tgt = s.target
+    val = _strip_cast(s.value)
+    if not (isinstance(val, BinOp) and val.op == "*") or len(tgt.indices) != 3:
+        return None
+    x, y = _strip_cast(val.lhs), _strip_cast(val.rhs)
+    if not (isinstance(x, Access) and isinstance(y, Access)):
+        return None
+    idx = list(nest._indices)
+    if not all(isinstance(q, Index) and any(q is w for w in idx) for q in tgt.indices) or len(set(map(id, tgt.indices))) != 3:
+        return None
+    k = [q for q in idx if not any(q is w for w in tgt.indices)][0]
+
+    def positions(acc, batch_ix, row_ix, col_ix):
+        """Positions of the three indices in the access, or None if it uses anything else / misses row or column."""
+        pos = {}
+        for d, q in enumerate(acc.indices):
+            for name, want in (("b", batch_ix), ("r", row_ix), ("c", col_ix)):
+                if q is want:
+                    if name in pos:
+                        return None
+                    pos[name] = d
+                    break
+            else:
+                return None
+        if "r" not in pos or "c" not in pos:
+            return None
+        return (pos.get("b"), pos["r"], pos["c"])
+
+    # C's indices are (b, i, j) in some order; which of them is the batch index follows from the operands:
+    # b appears in C and in at least one operand together with k, i only with A's k, j only with B's k
+    for b in tgt.indices:
+        i_j = [q for q in tgt.indices if q is not b]
+        for i, j in (i_j, i_j[::-1]):
+            for a_acc, b_acc in ((x, y), (y, x)):
+                pa, pb = positions(a_acc, b, i, k), positions(b_acc, b, k, j)
+                pc = positions(tgt, b, i, j)
+                if pa is None or pb is None or pc is None:
+                    continue
+                if pa[0] is None and pb[0] is None:
+                    continue          # no operand carries the batch index: not a batch matmul
+                return GemmSpec(a=a_acc.array, b=b_acc.array, c=tgt.array, bias=None, m=i.extent, n=j.extent,
+                                k=k.extent, a_transposed=False, b_transposed=False, batch=b.extent,
+                                a_pos=pa, b_pos=pb, c_pos=pc)
+    return None
+
+
 def _match_relu(nest: Nest, c: Array) -> bool:
     if len(nest.shape) != 2 or len(nest.statements) != 1:
         return False
@@ -153,6 +213,11 @@ def _match_bias(nest: Nest, c: Array) -> Optional[Array]:
 
 def _match_gemm(nests: List[Nest], partial: Optional[int], plan: Optional[Plan]) -> Optional[GemmSpec]:
     spec = _match_matmul(nests[0])
+    if spec is None:
+        spec = _match_batch_matmul(nests[0])
+        if spec is not None and len(nests) > 1:
+            raise UnsupportedNestError("a batch matmul takes its ReLU / scaling from tensorize(prologue_op=, epilogue_op=), "
+                                       "not from fused nests")
     if spec is None:
         return None
     rest = nests[1:]

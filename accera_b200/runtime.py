@@ -31,7 +31,7 @@ _COMPUTE = {"auto": COMPUTE_AUTO, "simt": COMPUTE_SIMT, "tensor": COMPUTE_TENSOR
             "tensor_preferred": COMPUTE_TENSOR_PREFERRED}
 
 EXPORTED_SYMBOLS = (
-    "accb_gemm", "accb_gemm_replicated", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_noalloc", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
+    "accb_gemm", "accb_gemm_batched", "accb_gemm_replicated", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_noalloc", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
     "accb_gather_rank2_dims", "accb_set_device", "accb_set_stream", "accb_synchronize", "accb_last_error",
     "accb_launch_count", "accb_release_workspace", "accb_device_count", "accb_version",
 )
@@ -73,6 +73,8 @@ def lib() -> ctypes.CDLL:
     vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32
     L.accb_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp]
     L.accb_gemm.restype = ctypes.c_int
+    L.accb_gemm_batched.argtypes = [ctypes.POINTER(GemmDesc), i64, i64, i64, i64, vp, vp, vp, vp]
+    L.accb_gemm_batched.restype = ctypes.c_int
     L.accb_gemm_replicated.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp), i32, vp]
     L.accb_gemm_replicated.restype = ctypes.c_int
     L.accb_reduce_mean_rank3.argtypes = [vp, i64, i64, i64, vp, i32]
@@ -194,15 +196,7 @@ def _sync_torch_stream(*arrays) -> None:
 # the three ops
 # ---------------------------------------------------------------------------
 
-def gemm(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: bool = False, compute: str = "auto",
-         kind: Optional[str] = None, out_kind: Optional[str] = None, max_ctas: int = 0) -> None:
-    """C <- epi(alpha * A @ B + beta * C + bias), in place in C.
-
-    A [M,K], B [K,N], C [M,N]; strides are taken from the arrays, so a Fortran-
-    ordered B is the reference's LAST_MAJOR layout.  `kind`/`out_kind` = "bfloat16"
-    marks uint16 numpy arrays as bf16 bit patterns.  `max_ctas` bounds the tensor-core kernel's persistent
-    grid (0 = every SM), to leave SMs for a collective that runs concurrently.
-    """
+def _gemm_args(A, B, C, bias, alpha, beta, relu, compute, kind, out_kind, max_ctas):
     pa, ta, sha, sta, da = _describe(A, kind)
     pb, tb, shb, stb, db = _describe(B, kind)
     pc, tc, shc, stc, dc = _describe(C, out_kind)
@@ -227,8 +221,87 @@ def gemm(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: boo
     d.alpha, d.beta = alpha, beta
     d.epilogue = EPI_RELU if relu else EPI_NONE
     d.max_ctas = int(max_ctas)
+    return d, pa, pb, pc, pbias
+
+
+def gemm(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: bool = False, compute: str = "auto",
+         kind: Optional[str] = None, out_kind: Optional[str] = None, max_ctas: int = 0) -> None:
+    """C <- epi(alpha * A @ B + beta * C + bias), in place in C.
+
+    A [M,K], B [K,N], C [M,N]; strides are taken from the arrays, so a Fortran-
+    ordered B is the reference's LAST_MAJOR layout.  `kind`/`out_kind` = "bfloat16"
+    marks uint16 numpy arrays as bf16 bit patterns.  `max_ctas` bounds the tensor-core kernel's persistent
+    grid (0 = every SM), to leave SMs for a collective that runs concurrently.
+    """
+    d, pa, pb, pc, pbias = _gemm_args(A, B, C, bias, alpha, beta, relu, compute, kind, out_kind, max_ctas)
     _sync_torch_stream(A, B, C)
     _check(lib().accb_gemm(ctypes.byref(d), pa, pb, pc, pbias))
+
+
+def gemm_call(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: bool = False, compute: str = "auto",
+              kind: Optional[str] = None, out_kind: Optional[str] = None, max_ctas: int = 0):
+    """-> a zero-argument callable that repeats this GEMM on the same arrays.
+
+    The descriptor is filled and the device / stream selected once, now; each later call is only the C-ABI call,
+    which is what a compiled HAT stub does (its descriptor is a constant).  For timing loops and for callers
+    that issue the same GEMM many times.  The arrays must stay alive and in place; for device tensors the stream
+    is torch's current stream at the time of THIS call.
+    """
+    d, pa, pb, pc, pbias = _gemm_args(A, B, C, bias, alpha, beta, relu, compute, kind, out_kind, max_ctas)
+    _sync_torch_stream(A, B, C)
+    fn = lib().accb_gemm
+    ref = ctypes.byref(d)
+    keep = (A, B, C, bias, d)
+
+    def call() -> None:
+        rc = fn(ref, pa, pb, pc, pbias)
+        if rc < 0:
+            _check(rc)
+    call.keep_alive = keep
+    return call
+
+
+def gemm_batched(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: bool = False,
+                 compute: str = "auto", kind: Optional[str] = None, out_kind: Optional[str] = None,
+                 max_ctas: int = 0) -> None:
+    """C[b] <- epi(alpha * A[b] @ B[b] + beta * C[b] + bias) for every b, in place in C.
+
+    A [batch, M, K], B [batch, K, N], C [batch, M, N]: rank-3 arrays whose first stride is the batch
+    stride; the other two are the matrix strides, as for `gemm`.  A or B may also be rank 2 (or have
+    batch stride 0, e.g. an expanded tensor): that operand is shared by all problems.
+    """
+    pa, ta, sha, sta, _ = _describe(A, kind)
+    pb, tb, shb, stb, _ = _describe(B, kind)
+    pc, tc, shc, stc, _ = _describe(C, out_kind)
+    if len(shc) != 3 or len(sha) not in (2, 3) or len(shb) not in (2, 3):
+        raise ValueError("gemm_batched: C must be rank 3, A and B rank 2 or 3")
+    batch, m, n = shc
+    if len(sha) == 2:
+        sha, sta = (batch,) + tuple(sha), (0,) + tuple(sta)
+    if len(shb) == 2:
+        shb, stb = (batch,) + tuple(shb), (0,) + tuple(stb)
+    k = sha[2]
+    if tuple(sha) != (batch, m, k) or tuple(shb) != (batch, k, n):
+        raise ValueError(f"shape mismatch: A{tuple(sha)} B{tuple(shb)} C{tuple(shc)}")
+    pbias = None
+    if bias is not None:
+        pbias, tbias, shbias, _, _ = _describe(bias)
+        if tbias != F32 or tuple(shbias) != (n,):
+            raise ValueError("bias must be fp32 of length N")
+    d = GemmDesc()
+    d.m, d.n, d.k = m, n, k
+    d.a_type, d.b_type, d.c_type = ta, tb, tc
+    d.compute = _COMPUTE[compute]
+    d.a_stride[0], d.a_stride[1] = max(sta[1], 1), max(sta[2], 1)
+    d.b_stride[0], d.b_stride[1] = max(stb[1], 1), max(stb[2], 1)
+    d.c_stride[0], d.c_stride[1] = max(stc[1], 1), max(stc[2], 1)
+    d.alpha, d.beta = alpha, beta
+    d.epilogue = EPI_RELU if relu else EPI_NONE
+    d.max_ctas = int(max_ctas)
+    # a batch of one problem has no meaningful batch stride (torch reports any value for a size-1 dimension)
+    a_bs, b_bs, c_bs = (0, 0, 0) if batch <= 1 else (sta[0], stb[0], stc[0])
+    _sync_torch_stream(A, B, C)
+    _check(lib().accb_gemm_batched(ctypes.byref(d), batch, a_bs, b_bs, c_bs, pa, pb, pc, pbias))
 
 
 def gemm_replicated(A, B, C_replicas, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: bool = False,

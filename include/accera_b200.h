@@ -95,6 +95,24 @@ typedef struct accb_gemm_desc {
 int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c, const float* bias);
 
 /*
+ * Batched GEMM: `batch` independent problems of the shape, types, strides and epilogue in `desc`,
+ *     C[b] <- epi(alpha * (A[b] @ B[b]) + beta * C[b] + bias[j]),   b = 0 .. batch-1,
+ * in one call (on the tensor cores: one persistent launch that walks all problems' tiles).
+ *
+ * Replaces the kernels the reference generates for the rank-3 nest
+ *     C[b, i, j] += A[b, i, k] * B[b, k, j]
+ * (accera/python/accera/test/mfma_tests.py:435-466; tensorised at :486-499).
+ * X[b] starts b * x_batch_stride elements after the base pointer; for the nest above with dense
+ * first-major arrays these are M*K, K*N and M*N.  a_batch_stride or b_batch_stride may be 0: that
+ * operand is then shared by all problems.  c_batch_stride must be at least the extent of one C.
+ * bias (n values, may be NULL) is shared by all problems.  The tensor-core path additionally needs
+ * batch strides of A and B that are multiples of 16 bytes; ACCB_COMPUTE_TENSOR_PREFERRED and
+ * ACCB_COMPUTE_AUTO fall back to the SIMT kernels otherwise.  Host or device pointers as for accb_gemm.
+ */
+int accb_gemm_batched(const accb_gemm_desc* desc, int64_t batch, int64_t a_batch_stride, int64_t b_batch_stride,
+                      int64_t c_batch_stride, const void* a, const void* b, void* c, const float* bias);
+
+/*
  * The same GEMM on the tensor cores, with the result stored to several replicas of C at once.
  * (No counterpart in the reference, which has no multi-GPU path.)  c_replicas[0] is the local C: it is
  * read when beta != 0 and written; c_replicas[1..n_replicas-1] receive the same values with the same

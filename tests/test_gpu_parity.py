@@ -619,3 +619,18 @@ def test_simt_f32_8x8_tiles_and_split_k(m, n, k):
     rt.gemm(A, B, got2, bias=bias, relu=True, compute="simt")
     _assert_close(got1, want, _gemm_scale(A, B) + np.abs(C0) + np.abs(bias), RTOL_F32, f"simt 8x8 {m}x{n}x{k}")
     assert np.array_equal(got1, got2)
+
+
+def test_host_c_view_with_padded_rows_keeps_the_gaps():
+    # C is a column range of a wider host array and beta = 0: the bytes between C's rows are not part of the
+    # result and must come back unchanged
+    rng = np.random.default_rng(31)
+    m, n, k, ld = 96, 80, 64, 112
+    A = rng.standard_normal((m, k), dtype=np.float32)
+    B = rng.standard_normal((k, n), dtype=np.float32)
+    wide = rng.standard_normal((m, ld), dtype=np.float32)
+    before = wide.copy()
+    rt.gemm(A, B, wide[:, :n], beta=0.0, compute="simt")
+    assert np.array_equal(wide[:, n:], before[:, n:])
+    want = oracle.gemm(A, B, np.zeros((m, n), np.float32), beta=0.0)
+    _assert_close(wide[:, :n], want, _gemm_scale(A, B), RTOL_F32, "padded C view")

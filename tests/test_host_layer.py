@@ -443,3 +443,110 @@ def test_gpu_target_functions_list_their_device_kernel(tmp_path):
     assert dev.provider == "libaccera_b200.so"
     _, fns = hat.load(hf.path)
     assert fns.names == [fn.name]                      # device functions are not host-callable
+
+
+def _batch_matmul_plan(batch, M, N, K, dtype=None, out_dtype=None, layouts=None, tensorize=True, epilogue_op=None):
+    """The reference's batch matmul test nest and schedule (mfma_tests.py:435-499), on static shapes."""
+    dtype = dtype or acc.ScalarType.float32
+    out_dtype = out_dtype or dtype
+    layouts = layouts or [acc.Layout.FIRST_MAJOR] * 3
+    A = acc.Array(role=acc.Role.INPUT, element_type=dtype, shape=(batch, M, K), layout=layouts[0])
+    B = acc.Array(role=acc.Role.INPUT, element_type=dtype, shape=(batch, K, N), layout=layouts[1])
+    C = acc.Array(role=acc.Role.INPUT_OUTPUT, element_type=out_dtype, shape=(batch, M, N), layout=layouts[2])
+    nest = acc.Nest(shape=(batch, M, N, K))
+    b, i, j, k = nest.get_indices()
+
+    @nest.iteration_logic
+    def _():
+        C[b, i, j] += A[b, i, k] * B[b, k, j]
+
+    schedule = nest.create_schedule()
+    ii, jj, kk = schedule.tile({i: 64, j: 64, k: 64})
+    target = acc.Target(acc.Target.Model.NVIDIA_B200)
+    if not tensorize:
+        return schedule.create_plan(target), (A, B, C)
+    shape = acc.MMAShape.M16xN16xK16_B1
+    splits = target.tensor_core_info.compute_tensor_splits(shape, 1)
+    iii, jjj, kkk = schedule.tile({ii: splits[0], jj: splits[1], kk: splits[2]})
+    plan, tensor_indices = schedule._create_tensorizable_plan(
+        target, block_indices=(i, j), warp_indices=(ii, jj), tensor_indices=(iii, jjj, kkk),
+        outer_nest_order=(b, i, j, k, ii, jj, kk))
+    kw = {"epilogue_op": epilogue_op} if epilogue_op is not None else {}
+    plan.tensorize(indices=tensor_indices, mma_shape=shape, **kw)
+    plan.cache(A, index=ii, location=target.MemorySpace.SHARED)
+    plan.cache(C, index=k, location=target.MemorySpace.MMA_FRAGMENT)
+    return plan, (A, B, C)
+
+
+def test_tensor_core_shape_helpers():
+    info = acc.Target(acc.Target.Model.NVIDIA_B200).tensor_core_info
+    assert info.mma_shape_to_tuple(acc.MMAShape.M16xN16xK16_B1) == (16, 16, 16)
+    assert info.mma_shape_to_tuple(acc.MMAShape.M64xN64xK1_B4) == (64, 64, 1)
+    assert info.mma_shape_to_tuple(acc.MMAShape.M32xN8xK16_B1) == (32, 8, 16)
+    assert info.compute_tensor_splits(acc.MMAShape.M16xN16xK4_B1, 4) == (16, 16, 16)
+
+
+def test_recognise_batch_matmul(tmp_path):
+    plan, (A, B, C) = _batch_matmul_plan(3, 128, 192, 256, acc.ScalarType.float16, acc.ScalarType.float32,
+                                         epilogue_op=acc.MMAFragmentOp.ReLU)
+    spec = patterns.recognise(plan)
+    assert spec.kind == "gemm" and spec.batch == 3 and (spec.m, spec.n, spec.k) == (128, 192, 256)
+    assert spec.a is A and spec.b is B and spec.c is C and spec.compute == "tensor" and spec.relu
+    assert spec.a_pos == (0, 1, 2) and spec.b_pos == (0, 1, 2) and spec.c_pos == (0, 1, 2)
+    pkg = acc.Package()
+    fn = pkg.add(plan, args=(A, B, C), base_name="bmm")
+    src = pkg._stub_source("bmm_pkg")
+    assert "accb_gemm_batched(&d, INT64_C(3), INT64_C(32768), INT64_C(49152), INT64_C(24576), a0, a1, a2, nullptr)" in src
+    assert "d.a_stride[0] = INT64_C(256); d.a_stride[1] = INT64_C(1);" in src
+    assert "d.b_stride[0] = INT64_C(192); d.b_stride[1] = INT64_C(1);" in src
+    assert "d.epilogue = ACCB_EPI_RELU" in src and "ACCB_COMPUTE_TENSOR_PREFERRED" in src
+    hat_path, lib_path = pkg.build("bmm_pkg", output_dir=str(tmp_path))[:2]
+    hf = hat.HATFile.read(hat_path)
+    f = hf.functions[0]
+    assert f.name == fn.name and [a.shape for a in f.arguments] == [[3, 128, 256], [3, 256, 192], [3, 128, 192]]
+    assert f.arguments[1].affine_map == [256 * 192, 192, 1]
+    lib = ctypes.CDLL(lib_path)
+    assert hasattr(lib, fn.name)
+
+
+def test_batch_matmul_layouts_and_shared_operand():
+    # last-major arrays: element (b, i, k) of A is at b + batch * (i + M * k)
+    plan, (A, B, C) = _batch_matmul_plan(4, 64, 64, 128, layouts=[acc.Layout.LAST_MAJOR, acc.Layout.FIRST_MAJOR,
+                                                                   acc.Layout.FIRST_MAJOR], tensorize=False)
+    pkg = acc.Package()
+    pkg.add(plan, args=(A, B, C), base_name="bmm_lm")
+    src = pkg._stub_source("p")
+    assert "d.a_stride[0] = INT64_C(4); d.a_stride[1] = INT64_C(256);" in src
+    assert "accb_gemm_batched(&d, INT64_C(4), INT64_C(1), INT64_C(8192), INT64_C(4096)" in src
+    assert "ACCB_COMPUTE_SIMT" in src                   # plain fp32 nest: true fp32 arithmetic
+
+    # B without the batch index is shared by all problems (batch stride 0); A indexed [b, k, i] is transposed
+    A = acc.Array(role=acc.Role.INPUT, element_type=acc.ScalarType.float16, shape=(5, 96, 32))
+    B = acc.Array(role=acc.Role.INPUT, element_type=acc.ScalarType.float16, shape=(96, 48))
+    C = acc.Array(role=acc.Role.INPUT_OUTPUT, element_type=acc.ScalarType.float16, shape=(5, 32, 48))
+    nest = acc.Nest(shape=(5, 32, 48, 96))
+    b, i, j, k = nest.get_indices()
+
+    @nest.iteration_logic
+    def _():
+        C[b, i, j] += A[b, k, i] * B[k, j]
+
+    spec = patterns.recognise(nest)
+    assert spec.batch == 5 and spec.a_pos == (0, 2, 1) and spec.b_pos == (None, 0, 1)
+    pkg = acc.Package()
+    pkg.add(nest, args=(A, B, C), base_name="bmm_shared")
+    src = pkg._stub_source("p")
+    assert "d.a_stride[0] = INT64_C(1); d.a_stride[1] = INT64_C(32);" in src
+    assert "accb_gemm_batched(&d, INT64_C(5), INT64_C(3072), INT64_C(0), INT64_C(1536)" in src
+
+    # neither operand carries the batch index: not a batch matmul
+    nest2 = acc.Nest(shape=(5, 32, 48, 96))
+    b, i, j, k = nest2.get_indices()
+    A2 = acc.Array(role=acc.Role.INPUT, element_type=acc.ScalarType.float16, shape=(32, 96))
+
+    @nest2.iteration_logic
+    def _():
+        C[b, i, j] += A2[i, k] * B[k, j]
+
+    with pytest.raises(patterns.UnsupportedNestError):
+        patterns.recognise(nest2)
