@@ -39,6 +39,7 @@
 #include <cuda_bf16.h>
 
 #include <atomic>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <type_traits>
@@ -104,6 +105,7 @@ struct UmmaParams {
     int batch;
     int a_batched, b_batched;
     int64_t c_bs;
+    int verbose;            // host only: print the launch plan to stderr (tuning override v=1)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -688,88 +690,100 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            const uint64_t pol_a = make_l2_policy(p.hint_a), pol_b = make_l2_policy(p.hint_b);
-            int tile_i = 0;
-            bool pacing = (p.pace_pct > 0) && leader;
-            for (int t = unit; t < num_tiles && ok; t += num_units, ++tile_i) {
-                int problem, tm, tn;
-                tile_coords_batched(t, p, problem, tm, tn);
-                const int row_a = (tm * kCtas + (int)rank) * kBlockM;
-                const int row_b = tn * BN + (TWO_SM ? (int)rank * (BN / 2) : 0);
-                if (pacing && tile_i > 0) {
-                    // Pacing, not a dependency: CTAs that drift apart stop finding each other's A / B panels in
-                    // L2 (they are re-read from DRAM instead).  Wait, for at most ~20 us, until most CTAs have
-                    // finished loading the previous round of tiles.
-                    const int target = (int)(((int64_t)tile_i * num_units * p.pace_pct) / 100);
-                    const long long t0 = clock64();
-                    bool in_time = true;
-                    while (*(volatile int*)p.pace < target && (in_time = (clock64() - t0 < 40000))) { }
-                    if (!in_time) pacing = false;      // the other CTAs are not running alongside: stop waiting for them
-                }
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % S;
-                    const uint32_t ph = (it / S) & 1u;
-                    if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, SITE_PRODUCER_EMPTY, kb)) { ok = false; break; }
-                    const uint32_t sa = smem_base + s * Plan::kStageBytes;
-                    const uint32_t sb = sa + Plan::kABytes;
-                    if constexpr (TWO_SM) {
-                        if (leader) mbar_arrive_expect_tx(full_bar(s), 2u * Plan::kStageBytes);
-                    } else {
-                        mbar_arrive_expect_tx(full_bar(s), (uint32_t)Plan::kStageBytes);
+            // The whole tile loop is instantiated once per operand layout / batching combination and the choice is
+            // made here, once: the k loop below then contains no layout-dependent branch or arithmetic.  (The loop
+            // issues two to six TMA loads per 0.3 us; anything that delays it starves the tensor pipe.)
+            auto produce = [&](auto a_mn_tag, auto b_mn_tag, auto batched_tag) {
+                constexpr bool A_MN = decltype(a_mn_tag)::value, B_MN = decltype(b_mn_tag)::value;
+                constexpr bool BATCHED = decltype(batched_tag)::value;
+                uint32_t it = 0;
+                bool ok = true;
+                const uint64_t pol_a = make_l2_policy(p.hint_a), pol_b = make_l2_policy(p.hint_b);
+                int tile_i = 0;
+                bool pacing = (p.pace_pct > 0) && leader;
+                for (int t = unit; t < num_tiles && ok; t += num_units, ++tile_i) {
+                    int problem = 0, tm, tn;
+                    if constexpr (BATCHED) tile_coords_batched(t, p, problem, tm, tn);
+                    else tile_coords(t, p, tm, tn);
+                    const int row_a = (tm * kCtas + (int)rank) * kBlockM;
+                    const int row_b = tn * BN + (TWO_SM ? (int)rank * (BN / 2) : 0);
+                    if (pacing && tile_i > 0) {
+                        // Pacing, not a dependency: CTAs that drift apart stop finding each other's A / B panels in
+                        // L2 (they are re-read from DRAM instead).  Wait, for at most ~20 us, until most CTAs have
+                        // finished loading the previous round of tiles.
+                        const int target = (int)(((int64_t)tile_i * num_units * p.pace_pct) / 100);
+                        const long long t0 = clock64();
+                        bool in_time = true;
+                        while (*(volatile int*)p.pace < target && (in_time = (clock64() - t0 < 40000))) { }
+                        if (!in_time) pacing = false;      // the other CTAs are not running alongside: stop waiting for them
                     }
-                    const uint32_t fb = full_bar(s);
-#define ACCB_LOAD_STAGE(AMN, BMN, BATCHED)                                                                        \
-    load_stage<KIND, TWO_SM, BN, AMN, BMN, BATCHED>(&map_a, &map_b, sa, sb, fb, kb, row_a, row_b, problem, p.a_batched, \
-                                                    p.b_batched, pol_a, pol_b)
-                    if (p.batch == 1) {
-                        if (layout == 0) ACCB_LOAD_STAGE(false, false, false);
-                        else if (layout == 1) ACCB_LOAD_STAGE(true, false, false);
-                        else if constexpr (kBMnOk) {
-                            if (layout == 2) ACCB_LOAD_STAGE(false, true, false);
-                            else ACCB_LOAD_STAGE(true, true, false);
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const int s = it % S;
+                        const uint32_t ph = (it / S) & 1u;
+                        if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, SITE_PRODUCER_EMPTY, kb)) { ok = false; break; }
+                        const uint32_t sa = smem_base + s * Plan::kStageBytes;
+                        const uint32_t sb = sa + Plan::kABytes;
+                        if constexpr (TWO_SM) {
+                            if (leader) mbar_arrive_expect_tx(full_bar(s), 2u * Plan::kStageBytes);
+                        } else {
+                            mbar_arrive_expect_tx(full_bar(s), (uint32_t)Plan::kStageBytes);
                         }
-                    } else {
-                        if (layout == 0) ACCB_LOAD_STAGE(false, false, true);
-                        else if (layout == 1) ACCB_LOAD_STAGE(true, false, true);
-                        else if constexpr (kBMnOk) {
-                            if (layout == 2) ACCB_LOAD_STAGE(false, true, true);
-                            else ACCB_LOAD_STAGE(true, true, true);
-                        }
+                        load_stage<KIND, TWO_SM, BN, A_MN, B_MN, BATCHED>(&map_a, &map_b, sa, sb, full_bar(s), kb, row_a, row_b,
+                                                                          problem, p.a_batched, p.b_batched, pol_a, pol_b);
                     }
-#undef ACCB_LOAD_STAGE
+                    if (p.pace_pct > 0 && leader && ok) atomicAdd(p.pace, 1);   // counted even after this CTA stopped waiting
                 }
-                if (p.pace_pct > 0 && leader && ok) atomicAdd(p.pace, 1);   // counted even after this CTA stopped waiting
+            };
+            using T = std::true_type;
+            using F = std::false_type;
+            if (p.batch == 1) {
+                if (layout == 0) produce(F{}, F{}, F{});
+                else if (layout == 1) produce(T{}, F{}, F{});
+                else if constexpr (kBMnOk) {
+                    if (layout == 2) produce(F{}, T{}, F{});
+                    else produce(T{}, T{}, F{});
+                }
+            } else {
+                if (layout == 0) produce(F{}, F{}, T{});
+                else if (layout == 1) produce(T{}, F{}, T{});
+                else if constexpr (kBMnOk) {
+                    if (layout == 2) produce(F{}, T{}, T{});
+                    else produce(T{}, T{}, T{});
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (rank 0 of a pair only) ----------------
         if (lane == 0 && leader) {
-            uint32_t it = 0;
-            int local = 0;
-            bool ok = true;
-            for (int t = unit; t < num_tiles && ok; t += num_units, ++local) {
-                const int buf = local & 1;
-                const uint32_t tph = (local >> 1) & 1u;
-                if (!mbar_wait(tmem_empty_bar(buf), tph ^ 1u, p.status, SITE_MMA_TMEM_EMPTY, local)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % S;
-                    const uint32_t ph = (it / S) & 1u;
-                    if (!mbar_wait(full_bar(s), ph, p.status, SITE_MMA_FULL, kb)) { ok = false; break; }
+            // as for the producer: one instantiation of the loop per operand layout, chosen once
+            auto issue = [&](auto a_mn_tag, auto b_mn_tag) {
+                constexpr bool A_MN = decltype(a_mn_tag)::value, B_MN = decltype(b_mn_tag)::value;
+                uint32_t it = 0;
+                int local = 0;
+                bool ok = true;
+                for (int t = unit; t < num_tiles && ok; t += num_units, ++local) {
+                    const int buf = local & 1;
+                    const uint32_t tph = (local >> 1) & 1u;
+                    if (!mbar_wait(tmem_empty_bar(buf), tph ^ 1u, p.status, SITE_MMA_TMEM_EMPTY, local)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t sa = smem_base + s * Plan::kStageBytes;
-                    const uint32_t sb = sa + Plan::kABytes;
-                    if (layout == 0) issue_stage<KIND, TWO_SM, false, false>(tmem_d, sa, sb, p.idesc, kb == 0);
-                    else if (layout == 1) issue_stage<KIND, TWO_SM, true, false>(tmem_d, sa, sb, p.idesc, kb == 0);
-                    else if (layout == 2) issue_stage<KIND, TWO_SM, false, true>(tmem_d, sa, sb, p.idesc, kb == 0);
-                    else issue_stage<KIND, TWO_SM, true, true>(tmem_d, sa, sb, p.idesc, kb == 0);
-                    umma_commit<TWO_SM>(empty_bar(s));            // frees the stage once these MMAs have read it
+                    const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const int s = it % S;
+                        const uint32_t ph = (it / S) & 1u;
+                        if (!mbar_wait(full_bar(s), ph, p.status, SITE_MMA_FULL, kb)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t sa = smem_base + s * Plan::kStageBytes;
+                        const uint32_t sb = sa + Plan::kABytes;
+                        issue_stage<KIND, TWO_SM, A_MN, B_MN>(tmem_d, sa, sb, p.idesc, kb == 0);
+                        umma_commit<TWO_SM>(empty_bar(s));            // frees the stage once these MMAs have read it
+                    }
+                    if (ok) umma_commit<TWO_SM>(tmem_full_bar(buf));  // accumulator complete
                 }
-                if (ok) umma_commit<TWO_SM>(tmem_full_bar(buf));  // accumulator complete
-            }
+            };
+            if (layout == 0) issue(std::false_type{}, std::false_type{});
+            else if (layout == 1) issue(std::true_type{}, std::false_type{});
+            else if (layout == 2) issue(std::false_type{}, std::true_type{});
+            else issue(std::true_type{}, std::true_type{});
         }
     } else {
         // ---------------- epilogue warps ----------------
@@ -1009,6 +1023,10 @@ int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap
         if (cap >= 1 && cap < units) units = cap;
     }
     if (units > num_tiles) units = num_tiles;
+    if (p.verbose)
+        fprintf(stderr, "tcgen05 GEMM %lld x %lld x %lld x %d: %s tiles of %d columns, %d tiles on %d %s, pacing %d%%\n",
+                (long long)p.m, (long long)p.n, (long long)p.k, p.batch, TWO_SM ? "pair" : "single-CTA", BN, num_tiles, units,
+                TWO_SM ? "pairs" : "CTAs", p.pace_pct);
     cfg.gridDim = dim3((unsigned)(units * (TWO_SM ? 2 : 1)));
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, cm, (TC*)g.c, g.bias, p);
     if (e != cudaSuccess) { *err = cudaGetErrorString(e); return ACCB_ERR_CUDA; }
@@ -1131,6 +1149,7 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
     const int64_t tiles_total = (int64_t)p.tiles_m * p.tiles_n * batch;
     const int64_t units_est = two_sm ? g.num_sms / 2 : g.num_sms;
     p.hint_a = 0; p.hint_b = 0; p.c_stream = 0;
+    p.verbose = 0;
     p.tma_store = (c_tma_storable(d, g.c) && batch == 1) ? 1 : 0;   // batched: C is written with plain stores
     p.n_replicas = 1 + g.n_extra_c;
     // Long launches: keep the persistent CTAs in step tile by tile.  Left alone they drift apart over a hundred
@@ -1140,7 +1159,7 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
     if (p.pace_pct && two_sm && p.tiles_m >= 32) p.group_m = 16;
     p.pace = g.status + kStatusWords;
     if (const char* tune = getenv("ACCB_GEMM_TUNE")) {
-        // tuning override for experiments: "g=<group_m>,a=<0|1|2>,b=<0|1|2>,c=<0|1>"
+        // tuning override for experiments: "g=<group_m>,a=<0|1|2>,b=<0|1|2>,c=<0|1>,t=<0|1>,s=<pace %>,n=<128|256>,v=<0|1 print the plan>"
         for (const char* q = tune; *q; ++q) {
             if (q[1] != '=') continue;
             const int v = atoi(q + 2);
@@ -1150,6 +1169,7 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
             else if (*q == 'c') p.c_stream = v;
             else if (*q == 't' && g.n_extra_c == 0) p.tma_store = v && p.tma_store;
             else if (*q == 's') p.pace_pct = v;
+            else if (*q == 'v') p.verbose = v;
         }
     }
     if (p.pace_pct > 0) {

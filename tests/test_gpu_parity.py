@@ -634,3 +634,39 @@ def test_host_c_view_with_padded_rows_keeps_the_gaps():
     assert np.array_equal(wide[:, n:], before[:, n:])
     want = oracle.gemm(A, B, np.zeros((m, n), np.float32), beta=0.0)
     _assert_close(wide[:, :n], want, _gemm_scale(A, B), RTOL_F32, "padded C view")
+
+
+# ---------------------------------------------------------------------------
+# tile counts that fill the last round of the persistent grid badly, and both tile widths
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("compute", TENSOR_MODES)
+@pytest.mark.parametrize("kind,out_kind", [("bfloat16", "bfloat16"), ("float16", "float32"), ("int8", "int32"), ("float32", "float32")])
+@pytest.mark.parametrize("m,n,k", [(1024, 1024, 2048),      # 16 pair tiles on 74 pairs
+                                   (2000, 1500, 1552),      # ragged everywhere
+                                   (768, 512, 4112),        # 6 tiles, K tail of 16
+                                   (4096, 5120, 1024)])     # 320 pair tiles = 4 rounds + 24
+def test_tensor_awkward_tile_counts(compute, kind, out_kind, m, n, k):
+    _tensor_case(kind, out_kind, m, n, k, compute, beta=1.0, relu=True, use_bias=(kind != "int8"), alpha=1.0 if kind == "int8" else 0.5)
+
+
+def test_tile_width_does_not_change_the_result(monkeypatch):
+    # 128- and 256-column tiles accumulate every output element over K in the same order: identical bits
+    import torch
+    dev = torch.device("cuda:0")
+    torch.manual_seed(9)
+    m, n, k = 1536, 1100, 2048
+    A8 = torch.randint(-128, 128, (m, k), device=dev, dtype=torch.int8)
+    B8 = torch.randint(-128, 128, (n, k), device=dev, dtype=torch.int8).t()
+    A = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    B = (torch.randn(n, k, device=dev) / k ** 0.5).to(torch.bfloat16).t()
+    for a, b, cdt in ((A8, B8, torch.int32), (A, B, torch.float32), (A, B, torch.bfloat16)):
+        for compute in TENSOR_MODES:
+            outs = []
+            for tune in ("n=256", "n=128"):
+                monkeypatch.setenv("ACCB_GEMM_TUNE", tune)
+                C = torch.zeros(m, n, device=dev, dtype=cdt)
+                rt.gemm(a, b, C, beta=0.0, compute=compute)
+                rt.synchronize()
+                outs.append(C.clone())
+            assert torch.equal(outs[0], outs[1]), (cdt, compute)
