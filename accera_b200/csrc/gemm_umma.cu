@@ -696,7 +696,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             auto produce = [&](auto a_mn_tag, auto b_mn_tag, auto batched_tag) {
                 constexpr bool A_MN = decltype(a_mn_tag)::value, B_MN = decltype(b_mn_tag)::value;
                 constexpr bool BATCHED = decltype(batched_tag)::value;
-                uint32_t it = 0;
+                int s = 0;            // pipeline stage and its phase bit, advanced without divisions
+                uint32_t ph = 0;
                 bool ok = true;
                 const uint64_t pol_a = make_l2_policy(p.hint_a), pol_b = make_l2_policy(p.hint_b);
                 int tile_i = 0;
@@ -717,9 +718,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         while (*(volatile int*)p.pace < target && (in_time = (clock64() - t0 < 40000))) { }
                         if (!in_time) pacing = false;      // the other CTAs are not running alongside: stop waiting for them
                     }
-                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                        const int s = it % S;
-                        const uint32_t ph = (it / S) & 1u;
+                    for (int kb = 0; kb < num_kb; ++kb) {
                         if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, SITE_PRODUCER_EMPTY, kb)) { ok = false; break; }
                         const uint32_t sa = smem_base + s * Plan::kStageBytes;
                         const uint32_t sb = sa + Plan::kABytes;
@@ -730,6 +729,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         }
                         load_stage<KIND, TWO_SM, BN, A_MN, B_MN, BATCHED>(&map_a, &map_b, sa, sb, full_bar(s), kb, row_a, row_b,
                                                                           problem, p.a_batched, p.b_batched, pol_a, pol_b);
+                        if (++s == S) { s = 0; ph ^= 1u; }
                     }
                     if (p.pace_pct > 0 && leader && ok) atomicAdd(p.pace, 1);   // counted even after this CTA stopped waiting
                 }
@@ -758,7 +758,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // as for the producer: one instantiation of the loop per operand layout, chosen once
             auto issue = [&](auto a_mn_tag, auto b_mn_tag) {
                 constexpr bool A_MN = decltype(a_mn_tag)::value, B_MN = decltype(b_mn_tag)::value;
-                uint32_t it = 0;
+                int s = 0;
+                uint32_t ph = 0;
                 int local = 0;
                 bool ok = true;
                 for (int t = unit; t < num_tiles && ok; t += num_units, ++local) {
@@ -767,15 +768,14 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (!mbar_wait(tmem_empty_bar(buf), tph ^ 1u, p.status, SITE_MMA_TMEM_EMPTY, local)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                        const int s = it % S;
-                        const uint32_t ph = (it / S) & 1u;
+                    for (int kb = 0; kb < num_kb; ++kb) {
                         if (!mbar_wait(full_bar(s), ph, p.status, SITE_MMA_FULL, kb)) { ok = false; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint32_t sa = smem_base + s * Plan::kStageBytes;
                         const uint32_t sb = sa + Plan::kABytes;
                         issue_stage<KIND, TWO_SM, A_MN, B_MN>(tmem_d, sa, sb, p.idesc, kb == 0);
                         umma_commit<TWO_SM>(empty_bar(s));            // frees the stage once these MMAs have read it
+                        if (++s == S) { s = 0; ph ^= 1u; }
                     }
                     if (ok) umma_commit<TWO_SM>(tmem_full_bar(buf));  // accumulator complete
                 }

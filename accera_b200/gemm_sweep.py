@@ -237,7 +237,7 @@ def run_shape(shape: GemmShape, type_letter: str = "h", compute: str = "tensor_p
 
 
 RESULT_COLUMNS = list(COLUMNS) + ["type", "out_type", "compute", "batch_size", "min_of_means_s", "mean_of_means_s", "tflops",
-                                  "max_rel_err", "torch_min_of_means_s", "torch_tflops"]
+                                  "max_rel_err", "torch_min_of_means_s", "torch_tflops", "error"]
 
 
 def write_results(records: Sequence[dict], stream) -> None:
@@ -269,10 +269,19 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if not shapes:
         print("no shapes in " + args.input, file=sys.stderr)
         return 1
+    from .runtime import AccbError
     records = []
     for s in shapes:
-        rec = run_shape(s, args.type, args.compute, batches=args.batches, batch_size=args.batch_size,
-                        warmup=args.warmup, check=not args.no_check, compare_torch=args.torch, out_letter=args.out_type)
+        try:
+            rec = run_shape(s, args.type, args.compute, batches=args.batches, batch_size=args.batch_size,
+                            warmup=args.warmup, check=not args.no_check, compare_torch=args.torch, out_letter=args.out_type)
+        except (AccbError, ValueError) as e:
+            # a row this type / compute mode cannot run (e.g. alpha != 1 with integer inputs) is reported, not fatal
+            rec = dict(zip(COLUMNS, s.as_row()))
+            rec.update(type=args.type, compute=args.compute, error=str(e))
+            records.append(rec)
+            print(f"{s.m}x{s.n}x{s.k} tA={int(s.transA)} tB={int(s.transB)}: skipped: {e}", file=sys.stderr)
+            continue
         records.append(rec)
         print(f"{s.m}x{s.n}x{s.k} tA={int(s.transA)} tB={int(s.transB)}: {rec['tflops']:.2f} TFLOP/s"
               + (f" (torch {rec['torch_tflops']:.2f})" if "torch_tflops" in rec else "")
