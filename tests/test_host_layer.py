@@ -550,3 +550,104 @@ def test_batch_matmul_layouts_and_shared_operand():
 
     with pytest.raises(patterns.UnsupportedNestError):
         patterns.recognise(nest2)
+
+
+def test_reader_accepts_the_reference_emitters_formatting(tmp_path):
+    """A function table laid out the way the reference's emitter prints it (the sample in
+    docs/Tutorials/Optimized_MatMul.md:176-187: single-quoted names, double-quoted enumerations, padded
+    arrays `[ 784, 128 ]`, an inline `return` table, unnamed arguments, an 8-hex-digit name suffix) inside
+    the header / TOML guard structure of HATEmitter.h:1197-1265, read back with this package's reader."""
+    text = """#pragma once
+#ifndef __sample_pkg__
+#define __sample_pkg__
+
+#ifdef TOML
+
+[description]
+comment = ''
+author = ''
+version = ''
+license_url = ''
+
+[functions]
+
+[functions.tiled_mm_py_0badc0de]
+name = 'tiled_mm_py_0badc0de'
+description = ''
+calling_convention = "cdecl"
+arguments = [
+    {name = '', description = '', logical_type = "affine_array", declared_type = 'float*', element_type = 'float', usage = "input_output", shape = [ 784, 128 ], affine_map = [ 128, 1 ], affine_offset = 0},
+    {name = '', description = '', logical_type = "affine_array", declared_type = 'float*', element_type = 'float', usage = "input_output", shape = [ 128, 512 ], affine_map = [ 512, 1 ], affine_offset = 0},
+    {name = '', description = '', logical_type = "affine_array", declared_type = 'float*', element_type = 'float', usage = "input_output", shape = [ 784, 512 ], affine_map = [ 512, 1 ], affine_offset = 0}
+]
+return = {name = '', description = '', logical_type = "void", declared_type = 'void', element_type = 'void', usage = "output"}
+
+[target]
+
+[target.required]
+os = "linux"
+
+[target.required.CPU]
+architecture = "x86_64"
+extensions = [ "AVX2", "FMA3" ]
+
+[dependencies]
+link_target = "sample_pkg.a"
+deploy_files = [  ]
+dynamic = [  ]
+
+[compiled_with]
+compiler = ''
+flags = ''
+crt = ''
+libraries = [  ]
+
+[declaration]
+code = '''
+#endif // TOML
+
+#if defined(__cplusplus)
+extern "C"
+{
+#endif // defined(__cplusplus)
+
+void tiled_mm_py_0badc0de(float*, float*, float*);
+
+#ifndef __tiled_mm_py_DEFINED__
+#define __tiled_mm_py_DEFINED__
+void (*tiled_mm_py)(float*, float*, float*) = tiled_mm_py_0badc0de;
+#endif
+
+#if defined(__cplusplus)
+} // extern "C"
+#endif // defined(__cplusplus)
+
+#ifdef TOML
+'''
+
+#endif // TOML
+
+#endif // __sample_pkg__
+"""
+    path = tmp_path / "sample_pkg.hat"
+    path.write_text(text)
+    hf = hat.HATFile.read(str(path))
+    assert hf.name == "sample_pkg" and [f.name for f in hf.functions] == ["tiled_mm_py_0badc0de"]
+    f = hf.functions[0]
+    assert f.calling_convention == "cdecl" and f.return_info.logical_type == "void"
+    assert [a.shape for a in f.arguments] == [[784, 128], [128, 512], [784, 512]]
+    assert [a.affine_map for a in f.arguments] == [[128, 1], [512, 1], [512, 1]]
+    assert all(a.usage == "input_output" and a.declared_type == "float*" and a.element_type == "float" for a in f.arguments)
+    assert f.c_declaration().replace(" ", "") == "voidtiled_mm_py_0badc0de(float*,float*,float*);"
+    assert hf.dependencies["link_target"] == "sample_pkg.a" and hf.target["required"]["CPU"]["extensions"] == ["AVX2", "FMA3"]
+    assert "void (*tiled_mm_py)(float*, float*, float*) = tiled_mm_py_0badc0de;" in hf.declaration_code
+    # the C side of the same file: a compiler sees only the declarations
+    src = tmp_path / "client.c"
+    src.write_text('#include "sample_pkg.hat"\nint main(void) { return tiled_mm_py == 0; }\n'
+                   'void tiled_mm_py_0badc0de(float* a, float* b, float* c) { (void)a; (void)b; (void)c; }\n')
+    subprocess.run(["gcc", "-c", str(src), "-o", str(tmp_path / "client.o")], check=True)
+    # and it survives a rewrite by this package's writer
+    out = tmp_path / "rewritten.hat"
+    hf.write(str(out))
+    again = hat.HATFile.read(str(out))
+    assert again.functions[0].arguments == f.arguments and again.dependencies == hf.dependencies
