@@ -69,7 +69,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -80,6 +80,14 @@ class ClockSampler:
     def _pump(self):
         for line in self.proc.stdout:
             self.lines.append((time.time(), line.strip()))
+
+    def wait_ready(self, timeout: float = 5.0) -> bool:
+        """Blocks until nvidia-smi has delivered its first sample (it needs a few hundred ms to start, longer than
+        a short timed region lasts)."""
+        t_end = time.time() + timeout
+        while self.proc is not None and not self.lines and time.time() < t_end and self.proc.poll() is None:
+            time.sleep(0.01)
+        return bool(self.lines)
 
     def mark(self):
         return time.time()
@@ -95,7 +103,7 @@ class ClockSampler:
             self.proc.kill()
         sm, smax, power, reasons = [], [], [], set()
         for ts, line in self.lines:
-            if t0 is not None and not (t0 - 0.05 <= ts <= t1 + 0.15):
+            if t0 is not None and not (t0 - 0.02 <= ts <= t1 + 0.03):
                 continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
@@ -369,6 +377,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        sampler.wait_ready()
+    if dist_on:
+        dist.barrier()
     ms_per_step, wall0, wall1, gpu_launches = timed_steps(step, args.steps, args.warmup, device, dist_on)
     rt.synchronize()
     clocks = sampler.stop(wall0, wall1) if rank == 0 else None
