@@ -118,3 +118,61 @@ def test_tensorized_plan_with_any_layout(tmp_path, a_layout, b_layout, c_layout)
     fns.mm(a, b, c)
     want = 5.0 * (a.astype(np.float64) @ b.astype(np.float64))        # alpha = 5, beta = 0 (mfma_tests.py:194)
     np.testing.assert_allclose(c, want, rtol=1e-3)
+
+
+def _tensorized_bf16_package(m, n, k, tmp_path, name):
+    A = acc.Array(role=acc.Role.INPUT, element_type=acc.ScalarType.bfloat16, shape=(m, k))
+    B = acc.Array(role=acc.Role.INPUT, element_type=acc.ScalarType.bfloat16, shape=(k, n), layout=acc.Array.Layout.LAST_MAJOR)
+    C = acc.Array(role=acc.Role.INPUT_OUTPUT, element_type=acc.ScalarType.bfloat16, shape=(m, n))
+    nest = acc.Nest((m, n, k))
+    i, j, kk = nest.get_indices()
+
+    @nest.iteration_logic
+    def _():
+        C[i, j] += A[i, kk] * B[kk, j]
+    plan = nest.create_schedule().create_plan(acc.Target(acc.Target.Model.NVIDIA_B200))
+    plan.tensorize(indices=(i, j, kk), mma_shape=acc.MMAShape.M16xN16xK16_B1, epilogue_op=acc.MMAFragmentOp.ReLU)
+    pkg = acc.Package()
+    fn = pkg.add(plan, args=(A, B, C), base_name="matmul_relu_bf16")
+    return pkg.build(name, output_dir=str(tmp_path))[0], fn.name
+
+
+def test_hat_function_on_device_tensors(tmp_path):
+    """The loader takes torch CUDA tensors for the arrays: used in place, on torch's current stream, no staging."""
+    import torch
+    m, n, k = 512, 384, 256
+    hat_path, name = _tensorized_bf16_package(m, n, k, tmp_path, "dev_pkg")
+    _, fns = hat.load(hat_path)
+    dev = torch.device("cuda:0")
+    torch.manual_seed(2)
+    A = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    B = (torch.randn(n, k, device=dev) / k ** 0.5).to(torch.bfloat16).t()          # column-major [k, n]
+    C = torch.randn(m, n, device=dev).to(torch.bfloat16)
+    want = torch.relu(A.float() @ B.float() + C.float())
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fns[name](A, B, C)
+    side.synchronize()
+    assert (C.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    # the descriptor is enforced for tensors too
+    with pytest.raises(ValueError):
+        fns[name](A, B.contiguous(), C)                                # row-major B where the package says column-major
+    with pytest.raises(TypeError):
+        fns[name](A.float(), B, C)
+    with pytest.raises(TypeError):
+        fns[name](A.cpu(), B, C)
+
+
+def test_run_benchmark_device_resident(tmp_path):
+    """hatlib times GPU functions on device-resident buffers; TFLOP/s of the reference's GEMM benchmarker is
+    2*M*N*K / min_of_means of that timing (accera_gemm.py:640-660)."""
+    m = n = k = 2048
+    hat_path, name = _tensorized_bf16_package(m, n, k, tmp_path, "bench_dev_pkg")
+    on_dev = hat.run_benchmark(hat_path, batch_size=5, min_time_in_sec=0.3, device_resident=True)
+    on_host = hat.run_benchmark(hat_path, batch_size=2, min_time_in_sec=0.3)
+    assert [r.function_name for r in on_dev] == [name]
+    t_dev, t_host = on_dev[0].min_of_means, on_host[0].min_of_means
+    tflops = 2.0 * m * n * k / t_dev * 1e-12
+    assert 0 < t_dev < t_host              # no PCIe staging in the device-resident timing
+    assert tflops > 100.0, tflops           # a 2048^3 bf16 GEMM on the tensor cores is far above any SIMT rate
