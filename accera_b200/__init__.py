@@ -1,4 +1,4 @@
-"""accera_b200: the HAT-exported GEMM(+ReLU) / reduce_mean / gather functions of Accera, re-implemented
+"""accera_b200: the HAT-exported GEMM(+ReLU) / reduce_mean / gather / range functions of Accera, re-implemented
 as hand-written sm_100a kernels behind the unchanged HAT surface.
 
     import accera_b200 as acc          # describes functions with the Accera DSL subset in accera_b200.lang
@@ -6,12 +6,13 @@ as hand-written sm_100a kernels behind the unchanged HAT surface.
     from accera_b200 import hat        # hat.load("name.hat"), hat.run_benchmark("name.hat")
 """
 from .lang import (AUTO, Array, CacheStrategy, Dimension, Layout, MMAFragmentOp, MMASchedulingPolicy, MMAShape, Nest, Plan,
-                   Role, ScalarType, Schedule, Target, _cast, _MemorySpace, abs, cast, create_dimensions, fuse, inf, max, min)
+                   Role, Scalar, ScalarType, Schedule, Target, _cast, _MemorySpace, abs, cast, ceil, create_dimensions, floor, fuse,
+                   inf, max, min)
 from .package import Package
 from .patterns import UnsupportedNestError
 
 __version__ = "0.1.0"
 
 __all__ = ["AUTO", "Array", "CacheStrategy", "Dimension", "Layout", "MMAFragmentOp", "MMASchedulingPolicy", "MMAShape", "Nest",
-           "Package", "Plan", "Role", "ScalarType", "Schedule", "Target", "UnsupportedNestError", "abs", "cast",
-           "create_dimensions", "fuse", "inf", "max", "min"]
+           "Package", "Plan", "Role", "Scalar", "ScalarType", "Schedule", "Target", "UnsupportedNestError", "abs", "cast",
+           "ceil", "create_dimensions", "floor", "fuse", "inf", "max", "min"]

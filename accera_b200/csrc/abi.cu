@@ -513,6 +513,52 @@ int accb_gather_rank2(const void* data, int64_t d0, int64_t d1, const int64_t* i
     return collect_status(s, stream);
 }
 
+int64_t accb_range_count_f32(float start, float limit, float delta)
+{
+    return range_count_f32(start, limit, delta);
+}
+
+int64_t accb_range_plan_f32(float start, float delta, int64_t n, int64_t* first, uint32_t* bits, int32_t* step,
+                            int64_t capacity, float* final_value)
+{
+    if (n < 0 || capacity < 0) return 0;
+    return range_plan_f32(start, delta, n, first, bits, step, capacity, final_value);
+}
+
+int accb_range_f32(int64_t n, float* output, float* start_inout, float delta)
+{
+    t_error.clear();
+    if (n < 0) return fail(ACCB_ERR_ARG, "accb_range_f32: negative length");
+    if (!start_inout) return fail(ACCB_ERR_ARG, "accb_range_f32: null start pointer");
+    if (n == 0) return ACCB_OK;
+    if (!output) return fail(ACCB_ERR_ARG, "accb_range_f32: null output pointer");
+    DeviceState* sp = nullptr;
+    int rc = device_state(&sp, nullptr);
+    if (rc != ACCB_OK) return rc;
+    DeviceState& s = *sp;
+    if (is_device_pointer(start_inout)) return fail(ACCB_ERR_ARG, "accb_range_f32: start_inout must be a host pointer");
+    const bool dev_out = is_device_pointer(output);
+    cudaStream_t stream = t_stream;
+    std::unique_lock<std::mutex> lock(s.mu, std::defer_lock);
+    float* dout = output;
+    if (!dev_out) {
+        lock.lock();
+        if ((rc = ensure(&s.slot[2], &s.slot_bytes[2], (size_t)n * 4)) != ACCB_OK) return rc;
+        dout = (float*)s.slot[2];
+    }
+    const char* err = "";
+    float last = *start_inout;
+    const int launched = launch_range_f32(n, dout, *start_inout, delta, &last, stream, &err);
+    if (launched < 0) return fail(launched, std::string("accb_range_f32: ") + err);
+    *start_inout = last;
+    if (!dev_out) {
+        cudaError_t e = cudaMemcpyAsync(output, dout, (size_t)n * 4, cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return fail_cuda("device to host copy", e);
+    }
+    return ACCB_OK;
+}
+
 int accb_set_device(int32_t device)
 {
     t_error.clear();

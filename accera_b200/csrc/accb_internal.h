@@ -61,6 +61,14 @@ int launch_reduce_mean(const float* data, int64_t d0, int64_t d1, int64_t d2, fl
 int launch_gather(const void* data, int64_t d0, int64_t d1, const int64_t* indices, int64_t i0, int64_t i1,
                   void* output, int axis, int elem_bytes, int* status, cudaStream_t stream, const char** err);
 
+// range.cu: output[i] = start + i rounded additions of delta (bit-identical to the serial recurrence); writes the
+// value after n additions to *final_value (host memory).  range_count_f32 is host-only.
+int64_t range_count_f32(float start, float limit, float delta);
+int64_t range_plan_f32(float start, float delta, int64_t n, int64_t* first, uint32_t* bits, int32_t* step, int64_t capacity,
+                       float* final_value);
+int launch_range_f32(int64_t n, float* output, float start, float delta, float* final_value, cudaStream_t stream,
+                     const char** err);
+
 // counts kernels launched (reported by accb_launch_count)
 void note_launches(int n);
 

@@ -309,6 +309,8 @@ def as_expr(v) -> Expr:
         return v
     if isinstance(v, Dimension):
         return DimExpr(v)
+    if isinstance(v, Scalar):
+        return ScalarRef(v)
     if isinstance(v, (int, float, bool)):
         return Const(v)
     raise TypeError(f"cannot use {type(v).__name__} in iteration logic")
@@ -337,6 +339,8 @@ def max(a, b): return Call("max", [as_expr(a), as_expr(b)])          # noqa: A00
 def min(a, b): return Call("min", [as_expr(a), as_expr(b)])          # noqa: A001
 def abs(a): return Call("abs", [as_expr(a)])                         # noqa: A001
 def cast(value, dtype: ScalarType): return Call("cast", [as_expr(value)], dtype)
+def floor(a): return Call("floor", [as_expr(a)])
+def ceil(a): return Call("ceil", [as_expr(a)])
 _cast = cast
 
 
@@ -362,6 +366,47 @@ class Dimension:
         return DimExpr(self) * as_expr(other)
 
     __rmul__ = __mul__
+
+
+class ScalarRef(Expr):
+    """A Scalar used as a value inside iteration logic."""
+    def __init__(self, scalar: "Scalar"):
+        self.scalar = scalar
+
+    def __repr__(self):
+        return self.scalar.name or "scalar"
+
+
+class Scalar:
+    """A scalar function argument (the reference's `accera._lang_python._lang.Scalar`, as the range-node tests use
+    it: dsl_tests.py:1438-1448): an INPUT scalar is passed by value, an INPUT_OUTPUT / OUTPUT one by pointer, a TEMP
+    one lives inside the package.  Arithmetic on it builds expressions; `.set(value)` assigns it."""
+    def __init__(self, type: ScalarType = ScalarType.float32, role: Role = Role.INPUT, name: str = "", value=None):
+        if isinstance(type, Role):          # Scalar(role) is not a form the reference has; keep the error early
+            raise TypeError("Scalar(type, role): the first argument is the element type")
+        self.type = type
+        self.element_type = type
+        self.role = role
+        self.name = name
+        self.value = value
+
+    def set(self, value) -> None:
+        _record(Statement("set_scalar", self, as_expr(value)))
+
+    def _bin(self, op, other, swap=False):
+        return ScalarRef(self)._bin(op, other, swap)
+
+    def __add__(self, o): return self._bin("+", o)
+    def __radd__(self, o): return self._bin("+", o, True)
+    def __sub__(self, o): return self._bin("-", o)
+    def __rsub__(self, o): return self._bin("-", o, True)
+    def __mul__(self, o): return self._bin("*", o)
+    def __rmul__(self, o): return self._bin("*", o, True)
+    def __truediv__(self, o): return self._bin("/", o)
+    def __rtruediv__(self, o): return self._bin("/", o, True)
+
+    def __repr__(self):
+        return f"Scalar({self.name or '?'}, {self.type.name}, {self.role.name})"
 
 
 def create_dimensions(role: Role = Role.INPUT) -> Tuple[Dimension, ...]:

@@ -26,7 +26,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 from . import lang, patterns
 from .hat import hat_file
-from .lang import Array, Dimension, Role, ScalarType, Target
+from .lang import Array, Dimension, Role, Scalar, ScalarType, Target
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 _INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
@@ -87,8 +87,10 @@ class Package:
         for a in args:
             if isinstance(a, Array) and a.role is Role.TEMP:
                 raise ValueError("TEMP arrays cannot be function arguments")      # Package.py:231-236
-            if not isinstance(a, (Array, Dimension)):
-                raise TypeError("args may contain Arrays and Dimensions")
+            if isinstance(a, Scalar) and a.role is Role.TEMP:
+                raise ValueError("TEMP scalars cannot be function arguments")
+            if not isinstance(a, (Array, Dimension, Scalar)):
+                raise TypeError("args may contain Arrays, Dimensions and Scalars")
         target = source.target if isinstance(source, lang.Plan) else Target.HOST
         for f in self._fns.values():
             if not target.is_compatible_with(f.target):
@@ -114,6 +116,8 @@ class Package:
             if isinstance(a, Array):
                 shape = tuple(s.name if isinstance(s, Dimension) else s for s in a.shape)
                 sig.append(str((a.role.name, a.element_type.name, shape, str(a.layout))))
+            elif isinstance(a, Scalar):
+                sig.append(str((a.role.name, a.type.name, "scalar")))
             else:
                 sig.append(str((a.name, a.type.name)))
         suffix = hashlib.md5(json.dumps(tuple(sig)).encode("utf-8")).digest().hex()[:16]
@@ -158,6 +162,26 @@ class Package:
                 raise patterns.UnsupportedNestError("gather indices must be index / int64")
             if spec.data.element_type is not spec.output.element_type:
                 raise patterns.UnsupportedNestError("gather output must have the data's element type")
+        elif spec.kind == "range_size":
+            for sc in (spec.start, spec.limit, spec.delta):
+                if not any(a is sc for a in args):
+                    raise ValueError(f"scalar {sc!r} is used by the nest but missing from args")
+                if sc.type is not ScalarType.float32 or sc.role is not Role.INPUT:
+                    raise patterns.UnsupportedNestError("range: start, limit and delta must be float32 input scalars")
+            if not any(a is spec.size for a in args) or spec.size.role is Role.INPUT:
+                raise ValueError("range size: the output Dimension must be an argument with Role.OUTPUT")
+        elif spec.kind == "range":
+            need(spec.output)
+            for sc in (spec.running, spec.delta):
+                if not any(a is sc for a in args):
+                    raise ValueError(f"scalar {sc!r} is used by the nest but missing from args")
+            if spec.output.element_type is not ScalarType.float32 or spec.running.type is not ScalarType.float32 \
+                    or spec.delta.type is not ScalarType.float32:
+                raise patterns.UnsupportedNestError("range is implemented for float32")
+            if spec.running.role is not Role.INPUT_OUTPUT or spec.delta.role is not Role.INPUT:
+                raise patterns.UnsupportedNestError("range: the running scalar must be INPUT_OUTPUT and delta INPUT")
+            if len(spec.output.shape) != 1:
+                raise patterns.UnsupportedNestError("range fills a one-dimensional array")
         elif spec.kind == "dims":
             for out, src in spec.assignments:
                 for d in (out, src):
@@ -305,6 +329,10 @@ class Package:
                                       declared_type=ctype + ("" if usage == "input" else "*"))
         ctype = lang.C_TYPE[a.element_type]
         usage = {Role.INPUT: "input", Role.INPUT_OUTPUT: "input_output", Role.OUTPUT: "output"}[a.role]
+        if isinstance(a, Scalar):
+            # element arguments that are not inputs are passed by pointer (HATEmitter.h:392-400)
+            return hat_file.Parameter(name=a.name, logical_type="element", usage=usage, element_type=ctype,
+                                      declared_type=ctype + ("" if usage == "input" else "*"))
         if a.is_dynamic:
             size = "*".join(s.name if isinstance(s, Dimension) else str(s) for s in a.shape)
             return hat_file.Parameter(name=a.name, logical_type="runtime_array", usage=usage, element_type=ctype,
@@ -323,6 +351,8 @@ class Package:
             return {"op": "reduce_mean", "axes": list(s.axes), "keepdims": int(s.keepdims)}
         if s.kind == "gather":
             return {"op": "gather", "axis": int(s.axis)}
+        if s.kind in ("range", "range_size"):
+            return {"op": s.kind}
         return {"op": "dims"}
 
     # ------------------------------------------------------ stub generation
@@ -347,6 +377,8 @@ class Package:
             arg_name[id(a)] = f"a{pos}"
             if isinstance(a, Dimension):
                 params.append(f"int64_t{'' if a.role is Role.INPUT else '*'} a{pos}")
+            elif isinstance(a, Scalar):
+                params.append(f"{lang.C_TYPE[a.element_type]}{'' if a.role is Role.INPUT else '*'} a{pos}")
             else:
                 params.append(f"{lang.C_TYPE[a.element_type]}* a{pos}")
 
@@ -406,6 +438,12 @@ class Package:
             body.append(f"    report(\"{fn.name}\", accb_gather_rank2({arg_name[id(s.data)]}, {d0}, {d1}, "
                         f"{arg_name[id(s.indices)]}, {i0}, {i1}, {arg_name[id(s.output)]}, {int(s.axis)}, "
                         f"{lang.TYPE_BYTES[s.data.element_type]}));")
+        elif s.kind == "range_size":
+            body.append(f"    *{arg_name[id(s.size)]} = accb_range_count_f32({arg_name[id(s.start)]}, {arg_name[id(s.limit)]}, "
+                        f"{arg_name[id(s.delta)]});")
+        elif s.kind == "range":
+            body.append(f"    report(\"{fn.name}\", accb_range_f32({dim(s.n)}, {arg_name[id(s.output)]}, "
+                        f"{arg_name[id(s.running)]}, {arg_name[id(s.delta)]}));")
         else:
             for out_dim, src in s.assignments:
                 body.append(f"    *{arg_name[id(out_dim)]} = {dim(src)};")

@@ -19,6 +19,8 @@ of each form in parentheses):
   gather          Output[i,j,k] = Data[Indices[i,j], k] | Data[i, Indices[j,k]]
                                                        (kernels/gather/naive_runtime_sized.py:26-49)
   dimension fn    Nest((1,)) whose logic only does OutDim.set(InDim)   (dsl_tests.py:1588-1594)
+  range size      Nest((1,)): OutDim.set(cast(floor((limit - start) / delta), int64))   (dsl_tests.py:1450-1454)
+  range           Nest([n]):  output[i] = s; s.set(s + delta)          (dsl_tests.py:1456-1462; s is an in/out Scalar)
 """
 from __future__ import annotations
 
@@ -26,7 +28,8 @@ import dataclasses
 from typing import Any, Dict, List, Optional, Tuple
 
 from . import lang
-from .lang import Access, Array, BinOp, Call, Const, DimExpr, Dimension, Index, MMAFragmentOp, Nest, Plan, Schedule, Statement
+from .lang import (Access, Array, BinOp, Call, Const, DimExpr, Dimension, Index, MMAFragmentOp, Nest, Plan, Scalar, ScalarRef,
+                   Schedule, Statement)
 
 
 class UnsupportedNestError(NotImplementedError):
@@ -73,6 +76,24 @@ class GatherSpec:
     output: Array
     axis: int
     kind: str = "gather"
+
+
+@dataclasses.dataclass
+class RangeSizeSpec:
+    start: Scalar
+    limit: Scalar
+    delta: Scalar
+    size: Dimension
+    kind: str = "range_size"
+
+
+@dataclasses.dataclass
+class RangeSpec:
+    output: Array
+    running: Scalar            # read as the first value, left as the value after the last addition
+    delta: Scalar
+    n: Any                     # int or Dimension
+    kind: str = "range"
 
 
 @dataclasses.dataclass
@@ -321,6 +342,51 @@ def _match_reduce_mean(nests: List[Nest], partial: Optional[int]) -> Optional[Re
     return ReduceMeanSpec(data=data, reduced=reduced, axes=tuple(axes), keepdims=keepdims)
 
 
+def _scalar_of(e) -> Optional[Scalar]:
+    e = _strip_cast(e)
+    return e.scalar if isinstance(e, ScalarRef) else None
+
+
+def _match_range_size(nest: Nest) -> Optional[RangeSizeSpec]:
+    if len(nest.statements) != 1 or nest.statements[0].kind != "set_dim":
+        return None
+    s = nest.statements[0]
+    v = _strip_cast(s.value)
+    if not (isinstance(v, Call) and v.fn == "floor"):
+        return None
+    q = _strip_cast(v.args[0])
+    if not (isinstance(q, BinOp) and q.op == "/"):
+        return None
+    span, delta = _strip_cast(q.lhs), _scalar_of(q.rhs)
+    if not (isinstance(span, BinOp) and span.op == "-") or delta is None:
+        return None
+    limit, start = _scalar_of(span.lhs), _scalar_of(span.rhs)
+    if limit is None or start is None:
+        return None
+    return RangeSizeSpec(start=start, limit=limit, delta=delta, size=s.target)
+
+
+def _match_range(nest: Nest) -> Optional[RangeSpec]:
+    if len(nest.shape) != 1 or len(nest.statements) != 2:
+        return None
+    s0, s1 = nest.statements
+    if not (s0.kind == "assign" and s0.op == "=" and s1.kind == "set_scalar"):
+        return None
+    if tuple(s0.target.indices) != tuple(nest._indices):
+        return None
+    running = _scalar_of(s0.value)
+    if running is None or s1.target is not running:
+        return None
+    v = _strip_cast(s1.value)
+    if not (isinstance(v, BinOp) and v.op == "+"):
+        return None
+    a, b = _scalar_of(v.lhs), _scalar_of(v.rhs)
+    delta = b if a is running else a if b is running else None
+    if delta is None or delta is running:
+        return None
+    return RangeSpec(output=s0.target.array, running=running, delta=delta, n=nest.shape[0])
+
+
 def _match_dims(nest: Nest) -> Optional[DimsSpec]:
     if not nest.statements or any(s.kind != "set_dim" for s in nest.statements):
         return None
@@ -346,6 +412,9 @@ def recognise(source) -> Any:
         raise TypeError("package.add takes a Nest, Schedule or Plan")
     nests = sched.nests
     if len(nests) == 1:
+        rs = _match_range_size(nests[0]) or _match_range(nests[0])
+        if rs is not None:
+            return rs
         d = _match_dims(nests[0])
         if d is not None:
             return d
@@ -360,5 +429,5 @@ def recognise(source) -> Any:
         return r
     logic = "; ".join(repr(s) for n in nests for s in n.statements)
     raise UnsupportedNestError(
-        "this package implements matmul(+bias)(+ReLU), reduce_mean and gather on B200 kernels and does not compile "
+        "this package implements matmul(+bias)(+ReLU), reduce_mean, gather and range on B200 kernels and does not compile "
         f"arbitrary loop nests; unrecognised logic: {logic}")

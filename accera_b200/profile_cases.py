@@ -4,6 +4,7 @@
     python -m accera_b200.profile_cases reduce_mean [--rows 8192 --cols 4096]
     python -m accera_b200.profile_cases gather [--table-rows 32000 --cols 4096 --indices 16384]
     python -m accera_b200.profile_cases matmul_relu_f32 [--m 512 --n 512 --k 512]
+    python -m accera_b200.profile_cases range [--elements 134217728]
 
 Sizes default to cases whose inputs exceed the 126 MB L2 while holding well under a
 few GB on the device, so that a multi-pass profiler capture stays short.
@@ -19,7 +20,8 @@ from . import runtime as rt
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm_bf16", "gemm_f16", "gemm_s8", "reduce_mean", "gather", "matmul_relu_f32"])
+    ap.add_argument("case", choices=["gemm_bf16", "gemm_f16", "gemm_s8", "reduce_mean", "gather", "matmul_relu_f32", "range"])
+    ap.add_argument("--elements", type=int, default=1 << 27)
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--n", type=int, default=None)
     ap.add_argument("--k", type=int, default=None)
@@ -50,6 +52,10 @@ def main() -> None:
         A = torch.rand(m, k, device=dev); B = torch.rand(k, n, device=dev); C = torch.zeros(m, n, device=dev)
         for _ in range(a.iters):
             rt.gemm(A, B, C, relu=True, compute="simt")
+    elif a.case == "range":
+        out = torch.empty(a.elements, device=dev)
+        for _ in range(a.iters):
+            rt.range_f32(out, 0.0, 0.001)
     elif a.case == "reduce_mean":
         x = torch.randn(1, a.rows, a.cols, device=dev)
         y = torch.empty(a.rows, device=dev)

@@ -32,7 +32,7 @@ _COMPUTE = {"auto": COMPUTE_AUTO, "simt": COMPUTE_SIMT, "tensor": COMPUTE_TENSOR
 
 EXPORTED_SYMBOLS = (
     "accb_gemm", "accb_gemm_batched", "accb_gemm_replicated", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_noalloc", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
-    "accb_gather_rank2_dims", "accb_set_device", "accb_set_stream", "accb_synchronize", "accb_last_error",
+    "accb_gather_rank2_dims", "accb_range_count_f32", "accb_range_f32", "accb_range_plan_f32", "accb_set_device", "accb_set_stream", "accb_synchronize", "accb_last_error",
     "accb_launch_count", "accb_release_workspace", "accb_device_count", "accb_version",
 )
 
@@ -87,6 +87,12 @@ def lib() -> ctypes.CDLL:
     L.accb_gather_rank2.restype = ctypes.c_int
     L.accb_gather_rank2_dims.argtypes = [i64, i64, i64, i64, i32, ctypes.POINTER(i64)]
     L.accb_gather_rank2_dims.restype = ctypes.c_int
+    L.accb_range_count_f32.argtypes = [ctypes.c_float, ctypes.c_float, ctypes.c_float]
+    L.accb_range_count_f32.restype = ctypes.c_int64
+    L.accb_range_plan_f32.argtypes = [ctypes.c_float, ctypes.c_float, i64, vp, vp, vp, i64, vp]
+    L.accb_range_plan_f32.restype = ctypes.c_int64
+    L.accb_range_f32.argtypes = [i64, vp, vp, ctypes.c_float]
+    L.accb_range_f32.restype = ctypes.c_int
     L.accb_set_device.argtypes = [i32]
     L.accb_set_device.restype = ctypes.c_int
     L.accb_set_stream.argtypes = [vp]
@@ -395,6 +401,36 @@ def gather_rank2(data, indices, output, axis: int = 0) -> None:
         raise TypeError("output element size differs from data element size")
     _sync_torch_stream(data, indices, output)
     _check(lib().accb_gather_rank2(pd, shd[0], shd[1], pi, shi[0], shi[1], po, int(axis), int(esize)))
+
+
+def range_count(start, limit, delta) -> int:
+    """Number of elements of Range(start, limit, delta): floor((limit - start) / delta) in fp32 (host only)."""
+    return int(lib().accb_range_count_f32(float(np.float32(start)), float(np.float32(limit)), float(np.float32(delta))))
+
+
+def range_plan(start, delta, n: int):
+    """-> (first[int64], bits[uint32], step[int32], final fp32): the segments of constant bit-pattern step that
+    the range kernel fills (host only; no GPU needed)."""
+    s, d = float(np.float32(start)), float(np.float32(delta))
+    final = np.zeros(1, dtype=np.float32)
+    count = int(lib().accb_range_plan_f32(s, d, int(n), None, None, None, 0, final.ctypes.data))
+    first = np.zeros(count, dtype=np.int64)
+    bits = np.zeros(count, dtype=np.uint32)
+    step = np.zeros(count, dtype=np.int32)
+    lib().accb_range_plan_f32(s, d, int(n), first.ctypes.data, bits.ctypes.data, step.ctypes.data, count, final.ctypes.data)
+    return first, bits, step, np.float32(final[0])
+
+
+def range_f32(output, start, delta) -> np.float32:
+    """Fills the 1-D fp32 `output` (numpy array or torch CUDA tensor) with start, start + delta, ... where every
+    addition is rounded to fp32 in index order; returns the running value after the last addition."""
+    ptr, shape, es = _raw(output)
+    if es != 4 or len(shape) != 1:
+        raise ValueError("range_f32 fills a one-dimensional fp32 array")
+    s = np.array([start], dtype=np.float32)
+    _sync_torch_stream(output)
+    _check(lib().accb_range_f32(int(shape[0]), ptr, s.ctypes.data, float(np.float32(delta))))
+    return np.float32(s[0])
 
 
 def gather_rank2_dims(d0: int, d1: int, i0: int, i1: int, axis: int):

@@ -266,6 +266,11 @@ def extras_single_gpu(device, peaks):
     b = 2 * 16384 * 4096 * 4 + 16384 * 8
     out["gather_f32_32000x4096_idx16384"] = {"us": t * 1e6, "GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / peaks["hbm_gbs"]}
     del T, idxs, outs
+    n_range = 1 << 27                                                            # 512 MiB written per launch
+    rbuf = torch.empty(n_range, device=device)
+    t = timeit([lambda: rt.range_f32(rbuf, 0.0, 0.001)], iters=20)
+    out["range_f32_2^27"] = {"us": t * 1e6, "GB/s": n_range * 4 / t / 1e9, "frac_hbm": n_range * 4 / t / 1e9 / peaks["hbm_gbs"]}
+    del rbuf
     A1 = torch.rand(512, 512, device=device); B1 = torch.rand(512, 512, device=device); C1 = torch.zeros(512, 512, device=device)
     t = timeit([lambda: rt.gemm(A1, B1, C1, relu=True, compute="simt")])            # 3 MiB: L2 resident by nature
     out["matmul_relu_f32_simt_512"] = {"us": t * 1e6, "TFLOP/s": 2 * 512 ** 3 / t / 1e12}

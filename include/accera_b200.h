@@ -188,6 +188,30 @@ int accb_gather_rank2(const void* data, int64_t d0, int64_t d1, const int64_t* i
 int accb_gather_rank2_dims(int64_t d0, int64_t d1, int64_t i0, int64_t i1, int32_t axis, int64_t* out_dims);
 
 /*
+ * Range (the ONNX operator), fp32.  Replaces the two functions of the reference's range-node test
+ * (accera/python/accera/test/dsl_tests.py:1436-1506; prototype kernels/range/naive_runtime_sized.py:11-41):
+ *   get_size:    *size = (int64) floor((limit - start) / delta), evaluated in fp32
+ *   get_result:  for i in [0, n): output[i] = *start; *start = *start + delta   (one rounded fp32 addition per
+ *                element, in index order; the scalar is an in/out argument and ends as the value after n additions)
+ * accb_range_f32 produces exactly the values of that serial loop, bit for bit, for any start, delta and n.
+ * `output` is a host or device pointer to n floats; `start_inout` is always a HOST pointer (it is the by-pointer
+ * scalar argument of the HAT prototype) and is updated before the call returns, also for device output.
+ * accb_range_count_f32 is host-only; a quotient that is negative, NaN or beyond int64 gives 0.
+ */
+int64_t accb_range_count_f32(float start, float limit, float delta);
+int accb_range_f32(int64_t n, float* output, float* start_inout, float delta);
+
+/*
+ * Host-only helper (no counterpart in the reference): the plan accb_range_f32 executes.  The n values of the serial
+ * loop fall into segments inside which consecutive fp32 BIT PATTERNS differ by a constant: element i of segment j
+ * (first[j] <= i < first[j+1], the last segment runs to n) has the bit pattern bits[j] + (i - first[j]) * step[j]
+ * (32-bit wrap-around arithmetic).  Writes at most `capacity` segments (any of the arrays may be NULL), returns the
+ * number of segments of the full plan, and stores the running value after n additions to *final_value if non-NULL.
+ */
+int64_t accb_range_plan_f32(float start, float delta, int64_t n, int64_t* first, uint32_t* bits, int32_t* step,
+                            int64_t capacity, float* final_value);
+
+/*
  * Runtime control.  These replace what the reference leaves to its loader
  * (device selection and synchronisation, tools/benchmarkers/accera_gemm.py:612-626)
  * and accera/runtime; none of them appears in a HAT prototype.

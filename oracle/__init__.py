@@ -1,4 +1,4 @@
-"""CPU oracle for the HAT GEMM(+ReLU) / reduce_mean / gather path.
+"""CPU oracle for the HAT GEMM(+ReLU) / reduce_mean / gather / range path.
 
 TEST INFRASTRUCTURE ONLY: tests, the smoke check and the timed CPU baseline of
 the benchmark use it as the checker; the product never imports it.
@@ -62,6 +62,10 @@ def lib(fast: bool = False) -> ctypes.CDLL:
         L.orc_gather_rank2.restype = None
         L.orc_gather_rank2_dims.argtypes = [i64, i64, i64, i64, ci, vp]
         L.orc_gather_rank2_dims.restype = None
+        L.orc_range_count_f32.argtypes = [f32, f32, f32]
+        L.orc_range_count_f32.restype = i64
+        L.orc_range_f32.argtypes = [i64, vp, vp, f32]
+        L.orc_range_f32.restype = None
         for n in ("orc_f32_to_bf16", "orc_bf16_to_f32", "orc_f32_to_f16", "orc_f16_to_f32"):
             getattr(L, n).argtypes = [vp, vp, i64]
             getattr(L, n).restype = None
@@ -185,6 +189,20 @@ def gather_rank2(data: np.ndarray, indices: np.ndarray, axis: int = 0, fast: boo
     L.orc_gather_rank2(data.ctypes.data, *data.shape, indices.ctypes.data, *indices.shape, out.ctypes.data, axis,
                        data.itemsize)
     return out
+
+
+def range_count(start, limit, delta) -> int:
+    """Number of elements of Range(start, limit, delta): floor((limit - start) / delta) in fp32."""
+    return int(lib().orc_range_count_f32(float(np.float32(start)), float(np.float32(limit)), float(np.float32(delta))))
+
+
+def range_f32(start, delta, n: int):
+    """-> (output[n], value of the running scalar after n additions): output[i] = start + delta + ... (i times),
+    every addition rounded to fp32 in index order."""
+    out = np.empty(int(n), dtype=np.float32)
+    s = np.array([start], dtype=np.float32)
+    lib().orc_range_f32(int(n), out.ctypes.data, s.ctypes.data, float(np.float32(delta)))
+    return out, np.float32(s[0])
 
 
 def max_threads() -> int:

@@ -303,6 +303,35 @@ void orc_gather_rank2_dims(int64_t d0, int64_t d1, int64_t i0, int64_t i1, int a
     else { out_dims[0] = d0; out_dims[1] = i0; out_dims[2] = i1; }
 }
 
+/*
+ * Range (the ONNX operator as the reference writes it).
+ *   size:   floor((limit - start) / delta) in fp32, cast to int64
+ *           (accera/python/accera/test/dsl_tests.py:1452-1454; kernels/range/naive_runtime_sized.py:21)
+ *   result: for i in [0, n): output[i] = start; start = start + delta      - one fp32 addition per element,
+ *           each rounded, in index order; the scalar is an in/out argument and ends as the value after n additions
+ *           (dsl_tests.py:1459-1462, 1490-1491; kernels/range/naive_runtime_sized.py:25-28, 52-54)
+ * A quotient that is negative, not finite or not representable gives size 0 (the reference leaves those undefined).
+ * The volatile keeps the additions separately rounded under any optimisation flags.
+ */
+int64_t orc_range_count_f32(float start, float limit, float delta)
+{
+    volatile float span = limit - start;
+    volatile float q = span / delta;
+    float f = floorf(q);
+    if (!(f >= 0.0f) || f >= 9.2e18f) return 0;
+    return (int64_t)f;
+}
+
+void orc_range_f32(int64_t n, float* output, float* start_inout, float delta)
+{
+    volatile float x = *start_inout;
+    for (int64_t i = 0; i < n; ++i) {
+        output[i] = x;
+        x = x + delta;
+    }
+    *start_inout = x;
+}
+
 /* conversions exported for the tests */
 void orc_f32_to_bf16(const float* src, uint16_t* dst, int64_t n) { for (int64_t i = 0; i < n; ++i) dst[i] = f32_to_bf16(src[i]); }
 void orc_bf16_to_f32(const uint16_t* src, float* dst, int64_t n) { for (int64_t i = 0; i < n; ++i) dst[i] = bf16_to_f32(src[i]); }

@@ -22,7 +22,9 @@ fused dimensions each nest runs, in order, over all of its remaining dimensions
 (docs/Reference/safety_analysis.md:28-34).  Arithmetic is done on numpy fp32 scalars so that
 every multiply and add is rounded separately, as the reference's un-vectorised HOST code does.
 
-Outputs: gather.npz, reduce_mean.npz, matmul_relu.npz (a few KB each).
+  range        kernels/range/naive_runtime_sized.py::generate_numpy - the reference's numpy loop, run as-is.
+
+Outputs: gather.npz, reduce_mean.npz, matmul_relu.npz, range.npz (a few KB to a few tens of KB each).
 """
 import importlib.util
 import itertools
@@ -127,6 +129,28 @@ def make_gather(ref):
     return out
 
 
+def make_range(ref):
+    """kernels/range/naive_runtime_sized.py::generate_numpy - the reference's own numpy loop for Range
+    (`output[i] = start; start += delta` on np.float32 scalars, size `int((limit - start) // delta)`), run on
+    the case of its verify() (1, 5, 2), on the case of dsl_tests.py:1479-1481 (1, 5, 0.5) and on ranges that
+    cross binades, run downwards, cross zero and stall (delta below half an ulp of the running value)."""
+    mod = load_reference_module(os.path.join(ref, "kernels", "range", "naive_runtime_sized.py"), "ref_range")
+    fn = mod.generate_numpy()
+    cases = {"verify": (1.0, 5.0, 2.0), "dsl_test": (1.0, 5.0, 0.5), "tenths": (0.0, 1000.3, 0.1),
+             "binades": (0.001, 300.0, 0.37), "down": (10.0, -3.0, -0.25), "cross_zero": (-7.3, 9.1, 0.013),
+             "thirds": (1.0, 4097.0, 1.0 / 3.0), "stall": (16777216.0, 16779000.0, 0.75), "tie": (8388608.0, 8390000.0, 0.5),
+             "tiny": (1e-40, 3e-38, 1.7e-41)}
+    out = {}
+    for name, (start, limit, delta) in cases.items():
+        s, l, d = np.float32(start), np.float32(limit), np.float32(delta)
+        with np.errstate(all="ignore"):
+            y = fn(s, l, d)
+        out[f"{name}_args"] = np.array([s, l, d], dtype=np.float32)
+        out[f"{name}_out"] = y
+    np.savez(os.path.join(HERE, "range.npz"), **out)
+    return out
+
+
 def make_reduce_mean(ref):
     mod = load_reference_module(os.path.join(ref, "kernels", "reduce_mean", "naive_runtime_sized.py"), "ref_reduce_mean")
     rng = np.random.default_rng(4102)
@@ -186,7 +210,8 @@ def main():
     g = make_gather(ref)
     r = make_reduce_mean(ref)
     m = make_matmul_relu(ref)
-    print(f"gather: {len(g)} arrays, reduce_mean: {len(r)} arrays, matmul_relu: {len(m)} arrays")
+    rg = make_range(ref)
+    print(f"gather: {len(g)} arrays, reduce_mean: {len(r)} arrays, matmul_relu: {len(m)} arrays, range: {len(rg)} arrays")
 
 
 if __name__ == "__main__":
