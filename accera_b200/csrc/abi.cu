@@ -52,6 +52,11 @@ struct DeviceState {
     size_t slot_bytes[4] = { 0, 0, 0, 0 };
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
+    // the scratch buffer is shared by all streams of the device: a launch that uses it on another stream than
+    // the previous user first waits (on the device) for that user's kernels
+    cudaEvent_t scratch_done = nullptr;
+    cudaStream_t scratch_stream = nullptr;
+    bool scratch_used = false;
     cudaStream_t pipe[2] = { nullptr, nullptr };   // staging pipeline of large host-pointer GEMMs
     cudaEvent_t pipe_ready = nullptr;              // B (and bias) have arrived
 };
@@ -452,9 +457,22 @@ int accb_reduce_mean_rank3(const float* data, int64_t d0, int64_t d1, int64_t d2
     }
     const size_t need = reduce_mean_scratch_bytes(d0, d1, d2, axes_mask, s.num_sms);
     if (need && (rc = ensure(&s.scratch, &s.scratch_bytes, need)) != ACCB_OK) return rc;
+    if (need) {
+        // order this launch after the previous user of the shared scratch buffer if that ran on another stream
+        cudaError_t e = cudaSuccess;
+        if (!s.scratch_done) e = cudaEventCreateWithFlags(&s.scratch_done, cudaEventDisableTiming);
+        if (e == cudaSuccess && s.scratch_used && s.scratch_stream != stream) e = cudaStreamWaitEvent(stream, s.scratch_done, 0);
+        if (e != cudaSuccess) return fail_cuda("ordering the scratch buffer between streams", e);
+    }
     const char* err = "";
     int n = launch_reduce_mean(din, d0, d1, d2, dout, axes_mask, (float*)s.scratch, s.scratch_bytes, s.num_sms, stream, &err);
     if (n < 0) return fail(n, std::string("accb_reduce_mean_rank3: ") + err);
+    if (need) {
+        cudaError_t e = cudaEventRecord(s.scratch_done, stream);
+        if (e != cudaSuccess) return fail_cuda("cudaEventRecord", e);
+        s.scratch_stream = stream;
+        s.scratch_used = true;
+    }
     if (!dev_in) {
         cudaError_t e = cudaMemcpyAsync(reduced, dout, (size_t)n_out * 4, cudaMemcpyDeviceToHost, stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(stream);

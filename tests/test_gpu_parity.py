@@ -670,3 +670,61 @@ def test_tile_width_does_not_change_the_result(monkeypatch):
                 rt.synchronize()
                 outs.append(C.clone())
             assert torch.equal(outs[0], outs[1]), (cdt, compute)
+
+
+def test_concurrent_threads_and_streams():
+    """Four host threads, each with its own stream and its own operands, issue tensor-core GEMMs, reductions and
+    gathers through the C ABI at the same time (the stream and the last error are per thread; pacing counters,
+    the reduction's scratch buffer and launch set-up are shared per device, the scratch buffer ordered between
+    streams by an event)."""
+    import threading
+    import torch
+    dev = torch.device("cuda:0")
+    torch.manual_seed(4)
+    m, n, k = 1024, 768, 512
+    jobs = []
+    for t in range(4):
+        A = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        B = (torch.randn(n, k, device=dev) / k ** 0.5).to(torch.bfloat16).t()
+        x = torch.randn(1, 8, 262144, device=dev) + t       # 8 outputs of 262144 elements: the split path with scratch
+        table = torch.randn(500, 1024, device=dev)
+        idx = torch.randint(0, 500, (64, 2), device=dev)
+        jobs.append((A, B, x, table, idx))
+    torch.cuda.synchronize()
+    results, errors = [None] * 4, []
+
+    def work(t):
+        try:
+            A, B, x, table, idx = jobs[t]
+            stream = torch.cuda.Stream(device=dev)
+            with torch.cuda.stream(stream):
+                outs = []
+                for rep in range(8):
+                    C = torch.zeros(m, n, device=dev, dtype=torch.float32)
+                    rt.gemm(A, B, C, beta=0.0, relu=True, compute="tensor_2sm" if rep % 2 else "tensor")
+                    red = torch.empty(1, 8, device=dev)
+                    rt.reduce_mean_rank3(x, red, [2])
+                    g = torch.empty(64, 2, 1024, device=dev)
+                    rt.gather_rank2(table, idx, g, 0)
+                    outs.append((C, red, g))
+                stream.synchronize()
+                rt.synchronize()
+            results[t] = outs
+        except Exception as e:          # noqa: BLE001 - reported below, in the main thread
+            errors.append((t, repr(e)))
+
+    threads = [threading.Thread(target=work, args=(t,)) for t in range(4)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
+    for t in range(4):
+        A, B, x, table, idx = jobs[t]
+        want_c = torch.relu(A.float() @ B.float())
+        want_r = x.mean(dim=2)
+        want_g = table[idx]
+        for C, red, g in results[t]:
+            assert (C - want_c).abs().max().item() <= 2e-2 * want_c.abs().max().item()
+            assert torch.allclose(red, want_r, rtol=1e-5, atol=1e-5)
+            assert torch.equal(g, want_g)
