@@ -396,7 +396,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             l0, l1 = plan.local_row_range(j)
             g0, g1 = plan.global_row_range(rank, j)
             gemm_fn(a_dev[l0:l1], b_dev, c_full[g0:g1])
-    kernel_ms, _, _, _ = timed_steps(gemm_only, args.steps, 1, device, dist_on)
+    if dist_on:
+        kernel_ms, _, _, _ = timed_steps(gemm_only, args.steps, 1, device, dist_on)
+    else:
+        # one GPU: a step IS one launch of the kernel (no gather), so the timed region above - CUDA events on the
+        # launching stream around exactly `steps` launches - is the kernel's average launch duration; a second
+        # loop would only sample a different point of the GPU's power / clock state
+        kernel_ms = ms_per_step
     kernel_tflops = (FLOPS / world) / (kernel_ms * 1e-3) / 1e12
 
     # end to end through the C ABI with host buffers (pinned): H2D of A, B, C; GEMM; D2H of C
