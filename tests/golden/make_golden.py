@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Generates the golden vectors in this directory from the reference's own Python sources.
 
-    python tests/golden/make_golden.py [/path/to/reference]      (default: /root/reference)
+    python tests/golden/make_golden.py /path/to/reference        (a checkout of the reference project)
 
 The reference stores no known-answer vectors for its matmul+ReLU, reduce_mean or gather functions,
 and its compiler cannot be built offline.  What it does hold, and what this script executes:
@@ -206,7 +206,9 @@ def make_matmul_relu(ref):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/reference")
+    ref = sys.argv[1]
     g = make_gather(ref)
     r = make_reduce_mean(ref)
     m = make_matmul_relu(ref)
