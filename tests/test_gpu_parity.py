@@ -740,3 +740,31 @@ def test_concurrent_threads_and_streams():
             assert (C - want_c).abs().max().item() <= 2e-2 * want_c.abs().max().item()
             assert torch.allclose(red, want_r, rtol=1e-5, atol=1e-5)
             assert torch.equal(g, want_g)
+
+
+def test_tutorial_known_answers():
+    """What the reference's compiled packages print in its tutorials (see tests/test_oracle_golden.py).  The fp32
+    kernels that do not split K start their accumulators from C and add the products in k order, as the reference's
+    nest does, and print the same digits; the cluster split-K kernel (chosen for 1024 x 512 x 256) adds C to the
+    folded partial sums and is one ulp away."""
+    from test_oracle_golden import TUTORIAL_OUTPUTS, tutorial_inputs
+    for m, n, k, printed in TUTORIAL_OUTPUTS:
+        A, B, C = tutorial_inputs(m, n, k)
+        want = oracle.gemm(A, B, C.copy(), beta=1.0)
+        got = C.copy()
+        rt.gemm(A, B, got, beta=1.0, compute="simt")
+        np.testing.assert_allclose(got, want, rtol=RTOL_F32)
+        values = {"%f" % v for v in got.ravel()}
+        if k == 128:
+            assert values == {printed}
+        else:
+            assert values <= {printed, "1536.420044"}
+    # the same sizes with column-major B take the generic kernel: accumulators from C there too
+    A, B, C = tutorial_inputs(784, 512, 128)
+    got = C.copy()
+    rt.gemm(A, np.asfortranarray(B), got, beta=1.0, compute="simt")
+    assert {"%f" % v for v in got.ravel()} == {"768.419983"}
+    A, B, C = tutorial_inputs(1024, 512, 256)
+    got = C.copy()
+    rt.gemm(A, np.asfortranarray(B), got, beta=1.0, compute="simt")
+    assert {"%f" % v for v in got.ravel()} == {"1536.419922"}

@@ -87,3 +87,26 @@ def test_alpha_beta_bias_semantics():
     np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-5)
     rows = oracle.gemm(A, B, C.copy(), rows=(2, 5))
     assert np.array_equal(rows[:2], C[:2]) and np.array_equal(rows[5:], C[5:]) and not np.array_equal(rows[2:5], C[2:5])
+
+
+# The only outputs of the reference's COMPILED packages that its tree holds: what its two matmul tutorials print.
+# A = 2, B = 3, C = 0.42 everywhere, C += A @ B in fp32.
+#   docs/Tutorials/Optimized_MatMul.md:277-280        HOST package, M=784 K=128 N=512:  768.419983
+#   docs/Tutorials/GPU/Hello_MatMul_GPU.md:277-281    GPU package,  M=1024 K=256 N=512: 1536.419922
+# The second value tells the accumulation order apart: adding the 256 products of 6 to 0.42 one by one gives
+# 1536.419922, summing the products first and adding 0.42 last gives 1536.420044.
+TUTORIAL_OUTPUTS = [(784, 512, 128, "768.419983"), (1024, 512, 256, "1536.419922")]
+
+
+def tutorial_inputs(m, n, k):
+    return (np.full((m, k), 2.0, np.float32), np.full((k, n), 3.0, np.float32), np.full((m, n), 0.42, np.float32))
+
+
+@pytest.mark.parametrize("m,n,k,printed", TUTORIAL_OUTPUTS)
+def test_oracle_reproduces_what_the_compiled_reference_prints(m, n, k, printed):
+    A, B, C = tutorial_inputs(m, n, k)
+    got = oracle.gemm(A, B, C, beta=1.0)
+    assert {"%f" % v for v in got.ravel()} == {printed}
+    if k == 256:
+        # the other order, for the record: it is NOT what the reference printed
+        assert "%f" % np.float32(np.float32(6.0 * k) + np.float32(0.42)) == "1536.420044"
