@@ -1,5 +1,5 @@
 /*
- * CPU oracle for the HAT GEMM(+ReLU) / reduce_mean / gather path.
+ * CPU oracle for the HAT GEMM(+ReLU) / reduce_mean / gather / range path.
  *
  * TEST INFRASTRUCTURE ONLY.  This file is a plain-C restatement of the loop
  * nests the reference (microsoft/Accera) compiles for its HOST target.  It is
@@ -18,15 +18,23 @@
  *   reduce_mean nests    kernels/reduce_mean/naive_runtime_sized.py:66-148
  *   gather nests         kernels/gather/naive_runtime_sized.py:26-49,
  *                        accera/python/accera/test/dsl_tests.py:1596-1601, 1642-1647
+ *   range nests          accera/python/accera/test/dsl_tests.py:1450-1462,
+ *                        kernels/range/naive_runtime_sized.py:21-28
  *
  * Pinning: the reference stores no golden vectors for this path.  The gather
  * functions are pinned against vectors produced by the reference's own numpy
  * loop restatement (kernels/gather/naive_runtime_sized.py:72-103) and the
  * reduce_mean / matmul+relu functions against vectors produced by executing the
  * reference's nest definitions under a small loop-nest interpreter; both sets
- * live in tests/golden/ with the script that made them.  The compiled HOST
- * package itself could not be built (needs a patched LLVM 15), so parity with
- * the *compiled* reference remains unpinned.
+ * live in tests/golden/ with the script that made them; range is pinned against
+ * the reference's own numpy loop (kernels/range/naive_runtime_sized.py:44-56) the
+ * same way.  The compiled HOST package itself could not be built (needs a patched
+ * LLVM 15).  The only outputs of compiled reference packages in its tree are the
+ * two values its matmul tutorials print (docs/Tutorials/Optimized_MatMul.md:277-280
+ * and docs/Tutorials/GPU/Hello_MatMul_GPU.md:277-281); orc_gemm_float reproduces
+ * both digit for digit, and the second one (1536.419922) fixes the accumulation
+ * order restated here (start from C, add the products in k order).  Beyond those
+ * two values parity with the *compiled* reference remains unpinned.
  *
  * Build: see oracle/Makefile.  The strict library is compiled without FMA
  * contraction so every fp32 sum is a sequence of separately rounded mul and add
