@@ -372,6 +372,28 @@ int accb_gemm_batched(const accb_gemm_desc* desc, int64_t batch, int64_t a_batch
     return gemm_entry("accb_gemm_batched", desc, batch, a_batch_stride, b_batch_stride, c_batch_stride, a, b, c, bias);
 }
 
+int accb_gemm_tile_plan(const accb_gemm_desc* desc, int64_t batch, int32_t num_sms, int32_t* cta_pairs, int32_t* tile_cols,
+                        int64_t* tiles, int64_t* rounds)
+{
+    t_error.clear();
+    if (!desc || !cta_pairs || !tile_cols || !tiles || !rounds) return fail(ACCB_ERR_ARG, "accb_gemm_tile_plan: null pointer");
+    if (desc->m < 1 || desc->n < 1 || desc->k < 1 || batch < 1 || num_sms < 2)
+        return fail(ACCB_ERR_ARG, "accb_gemm_tile_plan: sizes must be positive (num_sms >= 2)");
+    GemmLaunch g;
+    g.d = *desc;
+    g.a = g.b = nullptr; g.c = nullptr; g.bias = nullptr;
+    g.n_extra_c = 0;
+    g.batch = batch;
+    g.stream = nullptr; g.status = nullptr; g.device = -1;
+    g.num_sms = num_sms;
+    const int want = desc->compute == ACCB_COMPUTE_TENSOR ? 0 : desc->compute == ACCB_COMPUTE_TENSOR_2SM ? 1 : (desc->m > 128 ? -1 : 0);
+    int pairs = 0, cols = 0;
+    gemm_umma_tile_plan(g, want, &pairs, &cols, tiles, rounds);
+    *cta_pairs = pairs;
+    *tile_cols = cols;
+    return ACCB_OK;
+}
+
 int accb_gemm_replicated(const accb_gemm_desc* desc, const void* a, const void* b, void* const* c_replicas,
                          int32_t n_replicas, const float* bias)
 {

@@ -49,6 +49,8 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err);
 bool gemm_umma_supported(const GemmLaunch& g, const char** why);
 // want_two_sm: 1 = CTA pairs (cta_group::2), 0 = single CTAs, -1 = whichever tile shape suits the problem.
 int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err);
+// host only: the tile shape launch_gemm_umma would pick (from d, batch, num_sms, max_ctas) and the rounds of tiles it gives
+void gemm_umma_tile_plan(const GemmLaunch& g, int want_two_sm, int* two_sm, int* tile_cols, int64_t* tiles, int64_t* rounds);
 
 // reduce_mean.cu
 // Scratch (fp32 partial sums) a launch needs for these dims, in bytes; 0 when the

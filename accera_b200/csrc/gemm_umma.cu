@@ -1099,6 +1099,22 @@ TileChoice choose_tile(const GemmLaunch& g, int want_two_sm /* -1: free, 0 / 1: 
 
 }  // namespace
 
+void gemm_umma_tile_plan(const GemmLaunch& g, int want_two_sm, int* two_sm, int* tile_cols, int64_t* tiles, int64_t* rounds)
+{
+    const TileChoice t = choose_tile(g, want_two_sm);
+    const int64_t rows = t.two_sm ? 2 * kBlockM : kBlockM;
+    const int64_t batch = g.batch > 1 ? g.batch : 1;
+    const int64_t n_tiles = ((g.d.m + rows - 1) / rows) * ((g.d.n + t.bn - 1) / t.bn) * batch;
+    int64_t units = t.two_sm ? g.num_sms / 2 : g.num_sms;
+    if (g.d.max_ctas > 0 && g.d.max_ctas / (t.two_sm ? 2 : 1) >= 1 && g.d.max_ctas / (t.two_sm ? 2 : 1) < units)
+        units = g.d.max_ctas / (t.two_sm ? 2 : 1);
+    if (units < 1) units = 1;
+    *two_sm = t.two_sm ? 1 : 0;
+    *tile_cols = t.bn;
+    *tiles = n_tiles;
+    *rounds = (n_tiles + units - 1) / units;
+}
+
 bool gemm_umma_supported(const GemmLaunch& g, const char** why)
 {
     const accb_gemm_desc& d = g.d;

@@ -31,7 +31,7 @@ _COMPUTE = {"auto": COMPUTE_AUTO, "simt": COMPUTE_SIMT, "tensor": COMPUTE_TENSOR
             "tensor_preferred": COMPUTE_TENSOR_PREFERRED}
 
 EXPORTED_SYMBOLS = (
-    "accb_gemm", "accb_gemm_batched", "accb_gemm_replicated", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_noalloc", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
+    "accb_gemm", "accb_gemm_batched", "accb_gemm_tile_plan", "accb_gemm_replicated", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_noalloc", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
     "accb_gather_rank2_dims", "accb_range_count_f32", "accb_range_f32", "accb_range_plan_f32", "accb_set_device", "accb_set_stream", "accb_synchronize", "accb_last_error",
     "accb_launch_count", "accb_release_workspace", "accb_device_count", "accb_version",
 )
@@ -75,6 +75,9 @@ def lib() -> ctypes.CDLL:
     L.accb_gemm.restype = ctypes.c_int
     L.accb_gemm_batched.argtypes = [ctypes.POINTER(GemmDesc), i64, i64, i64, i64, vp, vp, vp, vp]
     L.accb_gemm_batched.restype = ctypes.c_int
+    L.accb_gemm_tile_plan.argtypes = [ctypes.POINTER(GemmDesc), i64, i32, ctypes.POINTER(i32), ctypes.POINTER(i32),
+                                      ctypes.POINTER(i64), ctypes.POINTER(i64)]
+    L.accb_gemm_tile_plan.restype = ctypes.c_int
     L.accb_gemm_replicated.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp), i32, vp]
     L.accb_gemm_replicated.restype = ctypes.c_int
     L.accb_reduce_mean_rank3.argtypes = [vp, i64, i64, i64, vp, i32]
@@ -242,6 +245,27 @@ def gemm(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: boo
     d, pa, pb, pc, pbias = _gemm_args(A, B, C, bias, alpha, beta, relu, compute, kind, out_kind, max_ctas)
     _sync_torch_stream(A, B, C)
     _check(lib().accb_gemm(ctypes.byref(d), pa, pb, pc, pbias))
+
+
+def gemm_tile_plan(m: int, n: int, k: int, *, in_type: str = "bfloat16", compute: str = "auto", batch: int = 1,
+                   num_sms: int = 148, b_row_major: bool = False, max_ctas: int = 0) -> dict:
+    """The tile shape the tensor-core path picks for an M x N x K problem (host only, no GPU needed):
+    {"cta_pairs", "tile_cols", "tiles", "rounds"}."""
+    d = GemmDesc()
+    d.m, d.n, d.k = m, n, k
+    t = {"bfloat16": BF16, "float16": F16, "float32": F32, "int8": S8, "uint8": U8}[in_type]
+    d.a_type = d.b_type = t
+    d.c_type = S32 if t in (S8, U8) else t
+    d.compute = _COMPUTE[compute]
+    d.a_stride[0], d.a_stride[1] = k, 1
+    d.b_stride[0], d.b_stride[1] = (n, 1) if b_row_major else (1, k)
+    d.c_stride[0], d.c_stride[1] = n, 1
+    d.alpha, d.beta, d.epilogue, d.max_ctas = 1.0, 0.0, EPI_NONE, int(max_ctas)
+    pairs, cols = ctypes.c_int32(), ctypes.c_int32()
+    tiles, rounds = ctypes.c_int64(), ctypes.c_int64()
+    _check(lib().accb_gemm_tile_plan(ctypes.byref(d), int(batch), int(num_sms), ctypes.byref(pairs), ctypes.byref(cols),
+                                     ctypes.byref(tiles), ctypes.byref(rounds)))
+    return {"cta_pairs": bool(pairs.value), "tile_cols": cols.value, "tiles": tiles.value, "rounds": rounds.value}
 
 
 def gemm_call(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: bool = False, compute: str = "auto",

@@ -113,6 +113,17 @@ int accb_gemm_batched(const accb_gemm_desc* desc, int64_t batch, int64_t a_batch
                       int64_t c_batch_stride, const void* a, const void* b, void* c, const float* bias);
 
 /*
+ * Host-only helper (no counterpart in the reference; touches no CUDA state, works without a GPU): the tile shape
+ * the tensor-core path picks for `desc` x `batch` on a device with `num_sms` SMs - *cta_pairs = 1 for 256-row tiles
+ * computed by two CTAs (cta_group::2), 0 for 128-row single-CTA tiles; *tile_cols = 256 or 128 - with the number of
+ * tiles and of rounds the persistent grid needs for them.  desc->compute fixes the CTA mode for ACCB_COMPUTE_TENSOR
+ * (single) and ACCB_COMPUTE_TENSOR_2SM (pairs) and leaves it to the cost model otherwise.  Returns ACCB_ERR_ARG for a
+ * null pointer or non-positive sizes.
+ */
+int accb_gemm_tile_plan(const accb_gemm_desc* desc, int64_t batch, int32_t num_sms, int32_t* cta_pairs, int32_t* tile_cols,
+                        int64_t* tiles, int64_t* rounds);
+
+/*
  * The same GEMM on the tensor cores, with the result stored to several replicas of C at once.
  * (No counterpart in the reference, which has no multi-GPU path.)  c_replicas[0] is the local C: it is
  * read when beta != 0 and written; c_replicas[1..n_replicas-1] receive the same values with the same

@@ -651,3 +651,24 @@ void (*tiled_mm_py)(float*, float*, float*) = tiled_mm_py_0badc0de;
     hf.write(str(out))
     again = hat.HATFile.read(str(out))
     assert again.functions[0].arguments == f.arguments and again.dependencies == hf.dependencies
+
+
+def test_gemm_tile_plan_is_host_only_and_follows_the_cost_model(monkeypatch):
+    monkeypatch.delenv("ACCB_GEMM_TUNE", raising=False)
+    plan = runtime.gemm_tile_plan
+    # the benchmark problem: 256 x 256 pair tiles, 8192 of them on 74 pairs
+    assert plan(65536, 8192, 8192) == {"cta_pairs": True, "tile_cols": 256, "tiles": 8192, "rounds": 111}
+    assert plan(4096, 4096, 4096)["rounds"] == 4 and plan(4096, 4096, 4096)["tile_cols"] == 256
+    # too small to give every SM a 256-column tile: single CTAs, 128 columns
+    assert plan(1024, 1024, 1024) == {"cta_pairs": False, "tile_cols": 128, "tiles": 64, "rounds": 1}
+    assert plan(256, 256, 256)["tile_cols"] == 128
+    # the compute mode fixes the CTA mode; the width is still chosen
+    assert plan(4096, 4096, 4096, compute="tensor") == {"cta_pairs": False, "tile_cols": 256, "tiles": 512, "rounds": 4}
+    assert plan(1024, 1024, 1024, compute="tensor_2sm")["cta_pairs"] is True
+    # 8-bit operands with a row-major B cannot use 128-column pair tiles (a 64-column share is narrower than a box)
+    assert plan(1024, 1024, 1024, in_type="int8", b_row_major=True, compute="tensor_2sm")["tile_cols"] == 256
+    # a batch multiplies the tiles; fewer SMs or a capped grid lengthen the rounds
+    assert plan(1024, 1024, 1024, batch=64) == {"cta_pairs": True, "tile_cols": 256, "tiles": 1024, "rounds": 14}
+    assert plan(8192, 8192, 8192, num_sms=132)["rounds"] == 16 and plan(8192, 8192, 8192, max_ctas=64)["rounds"] == 32
+    with pytest.raises(runtime.AccbError):
+        plan(0, 8, 8)
