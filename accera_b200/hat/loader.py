@@ -19,6 +19,7 @@ functions and what the reference's GEMM benchmarker reads its TFLOP/s from (acce
 from __future__ import annotations
 
 import ctypes
+import dataclasses
 import os
 import re
 import statistics
@@ -134,10 +135,14 @@ class HATFunction:
     def __call__(self, *args, device_id: Optional[int] = None):
         c_args, keep = self._marshal(args)
         tensors = [a for a in keep if _is_torch(a)]
+        from .. import runtime
         if tensors:
             # device buffers: the kernels go to torch's current stream of that device
-            from .. import runtime
             runtime._sync_torch_stream(*tensors)
+        elif device_id is not None:
+            # host arrays: staged through, and computed on, the GPU the caller names (hatlib's device_id argument,
+            # tools/benchmarkers/accera_gemm.py:614)
+            runtime.set_device(int(device_id))
         self._symbol(*c_args)
 
     def bind(self, *args):
@@ -236,25 +241,29 @@ def load(hat_path: str, try_dynamic_load: bool = True):
 # benchmarking (row fields as printed in docs/Tutorials/GPU/Hello_MatMul_GPU.md:207-209)
 # ---------------------------------------------------------------------------
 
+@dataclasses.dataclass
 class BenchmarkResult:
-    def __init__(self, function_name: str, batch_means: List[float]):
-        self.function_name = function_name
+    """hatlib's result record (the reference's benchmarker turns it into a dict with dataclasses.asdict and reads
+    min_of_means, tools/benchmarkers/accera_gemm.py:640-650).  All times are seconds per call."""
+    function_name: str
+    mean: float
+    median_of_means: float
+    mean_of_small_means: float
+    robust_mean: float
+    min_of_means: float
+
+    @staticmethod
+    def from_batch_means(function_name: str, batch_means: List[float]) -> "BenchmarkResult":
         means = sorted(batch_means)
-        self.mean = statistics.mean(means)
-        self.median_of_means = statistics.median(means)
         small = means[: max(1, len(means) // 2)]
-        self.mean_of_small_means = statistics.mean(small)
         trim = len(means) // 5
         core = means[trim: len(means) - trim] or means
-        self.robust_mean = statistics.mean(core)
-        self.min_of_means = means[0]
+        return BenchmarkResult(function_name=function_name, mean=statistics.mean(means),
+                               median_of_means=statistics.median(means), mean_of_small_means=statistics.mean(small),
+                               robust_mean=statistics.mean(core), min_of_means=means[0])
 
     def as_dict(self) -> Dict[str, Any]:
-        return {k: getattr(self, k) for k in ("function_name", "mean", "median_of_means", "mean_of_small_means",
-                                              "robust_mean", "min_of_means")}
-
-    def __repr__(self):
-        return repr(self.as_dict())
+        return dataclasses.asdict(self)
 
 
 def generate_arg_values(fn: Function, rng: np.random.Generator, dim_value: int = 128):
@@ -367,14 +376,14 @@ def run_benchmark(hat_path: str, store_in_hat: bool = False, batch_size: int = 1
         if functions and fn.name not in functions:
             continue
         if device_resident:
-            r = BenchmarkResult(fn.name, _run_benchmark_on_device(fn, rng, batch_size, min_time_in_sec,
+            r = BenchmarkResult.from_batch_means(fn.name, _run_benchmark_on_device(fn, rng, batch_size, min_time_in_sec,
                                                                   input_sets_minimum_size_MB, device_id))
             if verbose:
                 print(r.as_dict())
             results.append(r)
             continue
         args = generate_arg_values(fn.desc, rng)
-        fn(*args)                                      # warm-up (and first-touch of the staging workspace)
+        fn(*args, device_id=device_id)                 # warm-up (and first-touch of the staging workspace)
         batch_means: List[float] = []
         t_end = time.perf_counter() + float(min_time_in_sec)
         while len(batch_means) < 3 or time.perf_counter() < t_end:
@@ -384,7 +393,7 @@ def run_benchmark(hat_path: str, store_in_hat: bool = False, batch_size: int = 1
             batch_means.append((time.perf_counter() - t0) / batch_size)
             if len(batch_means) >= 100000:
                 break
-        r = BenchmarkResult(fn.name, batch_means)
+        r = BenchmarkResult.from_batch_means(fn.name, batch_means)
         if verbose:
             print(r.as_dict())
         results.append(r)

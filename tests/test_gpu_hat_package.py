@@ -24,9 +24,10 @@ def test_quickstart_package_end_to_end(tmp_path):
         np.testing.assert_allclose(C_test, C_numpy, atol=1e-3)                       # README.md:127-133
         want = oracle.gemm(A_test, B_test, np.zeros((512, 512), np.float32), relu=True)
         np.testing.assert_allclose(C_test, want, rtol=1e-5)
-    # C is INPUT_OUTPUT: a second call accumulates on top of the first result
+    # C is INPUT_OUTPUT: a second call accumulates on top of the first result; device_id names the GPU, as in
+    # the reference's benchmarker (tools/benchmarkers/accera_gemm.py:614)
     C2 = C_test.copy()
-    functions.matmul_relu_fusion_naive(A_test, B_test, C2)
+    functions.matmul_relu_fusion_naive(A_test, B_test, C2, device_id=0)
     np.testing.assert_allclose(C2, 2 * want, rtol=1e-5)
 
 
@@ -169,8 +170,8 @@ def test_run_benchmark_device_resident(tmp_path):
     2*M*N*K / min_of_means of that timing (accera_gemm.py:640-660)."""
     m = n = k = 2048
     hat_path, name = _tensorized_bf16_package(m, n, k, tmp_path, "bench_dev_pkg")
-    on_dev = hat.run_benchmark(hat_path, batch_size=5, min_time_in_sec=0.3, device_resident=True)
-    on_host = hat.run_benchmark(hat_path, batch_size=2, min_time_in_sec=0.3)
+    on_dev = hat.run_benchmark(hat_path, batch_size=5, min_time_in_sec=0.3, device_resident=True, device_id=0)
+    on_host = hat.run_benchmark(hat_path, batch_size=2, min_time_in_sec=0.3, device_id=0)
     assert [r.function_name for r in on_dev] == [name]
     t_dev, t_host = on_dev[0].min_of_means, on_host[0].min_of_means
     tflops = 2.0 * m * n * k / t_dev * 1e-12
