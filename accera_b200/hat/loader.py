@@ -365,17 +365,20 @@ def _run_benchmark_on_device(fn: "HATFunction", rng, batch_size: int, min_time_i
 
 def run_benchmark(hat_path: str, store_in_hat: bool = False, batch_size: int = 10, min_time_in_sec: float = 10,
                   input_sets_minimum_size_MB: int = 50, device_id: int = 0, verbose: bool = False,
-                  functions: Optional[List[str]] = None, device_resident: bool = False) -> List[BenchmarkResult]:
+                  functions: Optional[List[str]] = None, device_resident: Optional[bool] = None) -> List[BenchmarkResult]:
     """Times every function of the package: batches of `batch_size` calls until `min_time_in_sec` has
-    elapsed (at least 3 batches).  By default on host arrays, so each call includes the library's
-    host<->device staging; with device_resident=True on GPU-resident buffers, timed with CUDA events."""
+    elapsed (at least 3 batches).  device_resident=True times on GPU-resident buffers with CUDA events, False on
+    host arrays (each call then includes the library's host<->device staging).  The default follows hatlib: functions
+    of a GPU-target package (those that name the device kernel they launch) are timed on the device, the others on
+    host arrays."""
     _, fmap = load(hat_path)
     rng = np.random.default_rng(0)
     results = []
     for fn in fmap:
         if functions and fn.name not in functions:
             continue
-        if device_resident:
+        on_device = device_resident if device_resident is not None else bool(fn.desc.launches)
+        if on_device:
             r = BenchmarkResult.from_batch_means(fn.name, _run_benchmark_on_device(fn, rng, batch_size, min_time_in_sec,
                                                                   input_sets_minimum_size_MB, device_id))
             if verbose:

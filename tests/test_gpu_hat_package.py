@@ -171,7 +171,9 @@ def test_run_benchmark_device_resident(tmp_path):
     m = n = k = 2048
     hat_path, name = _tensorized_bf16_package(m, n, k, tmp_path, "bench_dev_pkg")
     on_dev = hat.run_benchmark(hat_path, batch_size=5, min_time_in_sec=0.3, device_resident=True, device_id=0)
-    on_host = hat.run_benchmark(hat_path, batch_size=2, min_time_in_sec=0.3, device_id=0)
+    on_host = hat.run_benchmark(hat_path, batch_size=2, min_time_in_sec=0.3, device_id=0, device_resident=False)
+    by_default = hat.run_benchmark(hat_path, batch_size=5, min_time_in_sec=0.3, device_id=0)   # a GPU-target package
+    assert by_default[0].min_of_means < 0.5 * on_host[0].min_of_means
     assert [r.function_name for r in on_dev] == [name]
     t_dev, t_host = on_dev[0].min_of_means, on_host[0].min_of_means
     tflops = 2.0 * m * n * k / t_dev * 1e-12
