@@ -28,7 +28,7 @@ from typing import Any, Dict, List, Optional
 
 import numpy as np
 
-from .hat_file import Function, HATFile, Parameter
+from .hat_file import Function, HATFile
 
 _NP_OF_C = {
     "float": np.float32, "double": np.float64, "float16_t": np.float16, "bfloat16_t": np.uint16,

@@ -25,11 +25,11 @@ of each form in parentheses):
 from __future__ import annotations
 
 import dataclasses
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, List, Optional, Tuple
 
 from . import lang
 from .lang import (Access, Array, BinOp, Call, Const, DimExpr, Dimension, Index, MMAFragmentOp, Nest, Plan, Scalar, ScalarRef,
-                   Schedule, Statement)
+                   Schedule)
 
 
 class UnsupportedNestError(NotImplementedError):

@@ -31,7 +31,6 @@ import itertools
 import os
 import re
 import sys
-import types
 
 import numpy as np
 

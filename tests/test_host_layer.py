@@ -11,7 +11,6 @@ import pytest
 
 import accera_b200 as acc
 from accera_b200 import hat, patterns, runtime
-from accera_b200.hat import hat_file
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 

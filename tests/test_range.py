@@ -6,13 +6,11 @@ bit-pattern step) expanded in numpy against the same vectors and against the ora
 recognition of the reference's range-node nests (dsl_tests.py:1436-1506) and the package they build.
 GPU tier: the kernel through the C ABI and through a HAT package, bit for bit against the oracle.
 """
-import ctypes
 import os
 
 import numpy as np
 import pytest
 
-import accera_b200 as acc
 import oracle
 from accera_b200 import hat, patterns, runtime as rt
 
