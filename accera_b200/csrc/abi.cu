@@ -20,9 +20,25 @@ namespace accb {
 static std::atomic<int64_t> g_launches{0};
 void note_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+int next_launch_id()
+{
+    static std::atomic<uint32_t> next{1};
+    for (;;) {
+        const int id = (int)(next.fetch_add(1, std::memory_order_relaxed) & 0x7fffffffu);
+        if (id != 0) return id;
+    }
+}
+
+Options& options()
+{
+    thread_local Options o;
+    return o;
+}
+
 namespace {
 
 constexpr int kMaxDevices = 64;
+constexpr int64_t kTileFlagInts = 1 << 18;   // 1 MiB of per-tile counters per device, shared by the replicated launches in flight
 
 thread_local std::string t_error;
 thread_local int t_device = -1;             // -1: use the current CUDA device
@@ -57,6 +73,9 @@ struct DeviceState {
     cudaEvent_t scratch_done = nullptr;
     cudaStream_t scratch_stream = nullptr;
     bool scratch_used = false;
+    // per-tile completion counters of replicated GEMM launches: a ring that launches take regions from
+    int* tile_flags = nullptr;
+    int64_t tile_flags_cursor = 0;
     cudaStream_t pipe[2] = { nullptr, nullptr };   // staging pipeline of large host-pointer GEMMs
     cudaEvent_t pipe_ready = nullptr;              // B (and bias) have arrived
 };
@@ -131,30 +150,62 @@ int ensure(void** buf, size_t* have, size_t need)
     return ACCB_OK;
 }
 
-// Reads the status words back (synchronises `stream`), clears them, and turns
-// them into an error code.
-int collect_status(DeviceState& s, cudaStream_t stream)
+// Reads the status words back (synchronises `stream`) and turns them into an error code.
+//   what = COLLECT_GEMM / COLLECT_GATHER: a synchronous host-pointer call asks about its own launches only
+//          (launch id `id`); a failure an earlier device-pointer launch left behind stays recorded for
+//          accb_synchronize and does not become this call's result.
+//   what = COLLECT_ALL: accb_synchronize reports whatever is recorded.
+// What is reported is cleared.
+enum { COLLECT_ALL = 0, COLLECT_GEMM = 1, COLLECT_GATHER = 2 };
+
+int decode_status(const int* w, int what, int id, bool* clear_gemm, bool* clear_gather, std::string* msg)
+{
+    *clear_gemm = *clear_gather = false;
+    const bool gemm_failed = w[ST_GEMM_ID] != 0 || w[ST_GEMM_COUNT] != 0;
+    const bool gemm_mine = what == COLLECT_ALL || (what == COLLECT_GEMM && w[ST_GEMM_ID] == id);
+    if (gemm_failed && gemm_mine) {
+        static const char* sites[] = { "?", "producer waiting for a free stage", "MMA waiting for operands",
+                                       "MMA waiting for a free accumulator", "epilogue waiting for the accumulator" };
+        const int site = (w[ST_GEMM_SITE] >> 24) & 0xff;
+        char buf[256];
+        snprintf(buf, sizeof buf, "tcgen05 GEMM (launch %d): bounded wait ran out (%s, block %d, step %d; %d wait(s) in all); "
+                 "results are invalid", w[ST_GEMM_ID], site >= 1 && site <= 4 ? sites[site] : sites[0],
+                 w[ST_GEMM_SITE] & 0xffffff, w[ST_GEMM_STEP], w[ST_GEMM_COUNT]);
+        *msg = buf;
+        *clear_gemm = true;
+        return ACCB_ERR_TIMEOUT;
+    }
+    const bool gather_mine = what == COLLECT_ALL || (what == COLLECT_GATHER && w[ST_GATHER_ID] == id);
+    if (w[ST_GATHER_COUNT] != 0 && gather_mine) {
+        char buf[200];
+        snprintf(buf, sizeof buf, "gather: %d index value(s) outside the data dimension; those elements were zero-filled",
+                 w[ST_GATHER_COUNT]);
+        *msg = buf;
+        *clear_gather = true;
+        return ACCB_ERR_INDEX;
+    }
+    return ACCB_OK;
+}
+
+int collect_status(DeviceState& s, cudaStream_t stream, int what = COLLECT_ALL, int id = 0)
 {
     cudaError_t e = cudaMemcpyAsync(s.status_host, s.status, kStatusWords * sizeof(int), cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return fail_cuda("kernel execution", e);
     int w[kStatusWords];
     memcpy(w, s.status_host, sizeof w);
-    if (w[0] == 0 && w[1] == 0) return ACCB_OK;
-    e = cudaMemsetAsync(s.status, 0, kStatusWords * sizeof(int), stream);
+    bool clear_gemm = false, clear_gather = false;
+    std::string msg;
+    const int rc = decode_status(w, what, id, &clear_gemm, &clear_gather, &msg);
+    if (rc == ACCB_OK) return ACCB_OK;
+    if (clear_gemm) e = cudaMemsetAsync(s.status + ST_GEMM_SITE, 0, 4 * sizeof(int), stream);      // words 1..4
+    if (clear_gather && e == cudaSuccess) {
+        e = cudaMemsetAsync(s.status + ST_GATHER_COUNT, 0, sizeof(int), stream);
+        if (e == cudaSuccess) e = cudaMemsetAsync(s.status + ST_GATHER_ID, 0, sizeof(int), stream);
+    }
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return fail_cuda("cudaMemsetAsync(status)", e);
-    char buf[200];
-    if (w[1] != 0) {
-        static const char* sites[] = { "?", "producer waiting for a free stage", "MMA waiting for operands",
-                                       "MMA waiting for a free accumulator", "epilogue waiting for the accumulator" };
-        const int site = (w[1] >> 24) & 0xff;
-        snprintf(buf, sizeof buf, "tcgen05 GEMM: bounded wait ran out (%s, block %d, step %d); results are invalid",
-                 site >= 1 && site <= 4 ? sites[site] : sites[0], w[1] & 0xffffff, w[2]);
-        return fail(ACCB_ERR_TIMEOUT, buf);
-    }
-    snprintf(buf, sizeof buf, "gather: %d index value(s) outside the data dimension; those elements were zero-filled", w[0]);
-    return fail(ACCB_ERR_INDEX, buf);
+    return fail(rc, msg);
 }
 
 size_t type_bytes(int t)
@@ -177,6 +228,8 @@ int64_t span_elems(int64_t d0, int64_t d1, const int64_t* st)
 }  // namespace
 
 int set_error(int code, const char* msg) { return fail(code, msg ? msg : ""); }
+void clear_error() { t_error.clear(); }
+int selected_device(int* dev) { return current_device(dev); }
 
 namespace {
 
@@ -213,11 +266,11 @@ int pipelined_host_gemm(DeviceState& s, GemmLaunch g, const void* a, const void*
     if (e == cudaSuccess && !s.pipe_ready) e = cudaEventCreateWithFlags(&s.pipe_ready, cudaEventDisableTiming);
     if (e != cudaSuccess) return fail_cuda("creating the staging pipeline", e);
 
-    // 16 row chunks by default (ACCB_STAGE_CHUNKS overrides, for experiments): the copy in of the first chunk and
+    // 16 row chunks by default (the host_stage_chunks option overrides): the copy in of the first chunk and
     // the copy out of the last one are the part of the pipeline that nothing overlaps.  Measured on
     // 65536 x 8192 x 8192 bf16: 47.7 ms with 8 chunks, 46.0 with 12 or 16, 46.4 with 32.
     int64_t parts = 16;
-    if (const char* env = getenv("ACCB_STAGE_CHUNKS")) { const int v = atoi(env); if (v >= 1 && v <= 256) parts = v; }
+    if (const int v = options().host_stage_chunks; v >= 1 && v <= 256) parts = v;
     int64_t chunk = (d.m + parts - 1) / parts;
     chunk = (chunk + 255) / 256 * 256;
     if (chunk < 1024) chunk = 1024;
@@ -258,7 +311,7 @@ int pipelined_host_gemm(DeviceState& s, GemmLaunch g, const void* a, const void*
     e = cudaStreamSynchronize(s.pipe[0]);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s.pipe[1]);
     if (e != cudaSuccess) return fail_cuda("kernel execution", e);
-    return collect_status(s, s.pipe[0]);
+    return collect_status(s, s.pipe[0], COLLECT_GEMM, g.launch_id);
 }
 
 }  // namespace
@@ -313,6 +366,7 @@ static int gemm_entry(const char* fn, const accb_gemm_desc* desc, int64_t batch,
     g.c_batch_stride = batch > 1 ? c_bs : 0;
     g.stream = t_stream;
     g.status = s.status;
+    g.launch_id = next_launch_id();
     g.device = dev;
     g.num_sms = s.num_sms;
 
@@ -356,7 +410,7 @@ static int gemm_entry(const char* fn, const accb_gemm_desc* desc, int64_t batch,
     if (all_host) {
         cudaError_t e = cudaMemcpyAsync(c, s.slot[2], bytes_c, cudaMemcpyDeviceToHost, g.stream);
         if (e != cudaSuccess) return fail_cuda("device to host copy", e);
-        return collect_status(s, g.stream);
+        return collect_status(s, g.stream, COLLECT_GEMM, g.launch_id);
     }
     return ACCB_OK;
 }
@@ -384,13 +438,60 @@ int accb_gemm_tile_plan(const accb_gemm_desc* desc, int64_t batch, int32_t num_s
     g.a = g.b = nullptr; g.c = nullptr; g.bias = nullptr;
     g.n_extra_c = 0;
     g.batch = batch;
-    g.stream = nullptr; g.status = nullptr; g.device = -1;
+    g.stream = nullptr; g.status = nullptr; g.device = -1; g.launch_id = 0;
     g.num_sms = num_sms;
     const int want = desc->compute == ACCB_COMPUTE_TENSOR ? 0 : desc->compute == ACCB_COMPUTE_TENSOR_2SM ? 1 : (desc->m > 128 ? -1 : 0);
     int pairs = 0, cols = 0;
     gemm_umma_tile_plan(g, want, &pairs, &cols, tiles, rounds);
     *cta_pairs = pairs;
     *tile_cols = cols;
+    return ACCB_OK;
+}
+
+int accb_gemm_launch_geometry(const accb_gemm_desc* desc, int64_t batch, int32_t num_sms, int32_t* grid, int32_t* block,
+                              int32_t* dynamic_shared_mem_bytes)
+{
+    t_error.clear();
+    if (!desc || !grid || !block || !dynamic_shared_mem_bytes) return fail(ACCB_ERR_ARG, "accb_gemm_launch_geometry: null pointer");
+    if (desc->m < 1 || desc->n < 1 || desc->k < 1 || batch < 1 || num_sms < 2)
+        return fail(ACCB_ERR_ARG, "accb_gemm_launch_geometry: sizes must be positive (num_sms >= 2)");
+    GemmLaunch g;
+    g.d = *desc;
+    g.a = g.b = nullptr; g.c = nullptr; g.bias = nullptr;
+    g.n_extra_c = 0;
+    g.batch = batch;
+    g.stream = nullptr; g.status = nullptr; g.device = -1; g.launch_id = 0;
+    g.num_sms = num_sms;
+    const int want = desc->compute == ACCB_COMPUTE_TENSOR ? 0 : desc->compute == ACCB_COMPUTE_TENSOR_2SM ? 1 : (desc->m > 128 ? -1 : 0);
+    int32_t out[8];
+    gemm_umma_launch_geometry(g, want, out);
+    for (int i = 0; i < 3; ++i) { grid[i] = out[i]; block[i] = out[3 + i]; }
+    *dynamic_shared_mem_bytes = out[6];
+    return ACCB_OK;
+}
+
+int accb_set_option(const char* name, int64_t value)
+{
+    t_error.clear();
+    if (!name) return fail(ACCB_ERR_ARG, "accb_set_option: null name");
+    Options& o = options();
+    const std::string n(name);
+    const int v = (int)value;
+    if (n == "reset") { o = Options(); return ACCB_OK; }
+    if (n == "gemm.tile_cols") { if (v != 0 && v != 128 && v != 256) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.tile_cols is 0, 128 or 256"); o.gemm_tile_cols = v; }
+    else if (n == "gemm.staged_store") o.gemm_staged_store = v < 0 ? -1 : (v ? 1 : 0);
+    else if (n == "gemm.pace_pct") { if (v > 100) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.pace_pct is -1 or 0..100"); o.gemm_pace_pct = v < 0 ? -1 : v; }
+    else if (n == "gemm.group_m") { if (v < 0 || v > 4096) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.group_m is 0..4096"); o.gemm_group_m = v; }
+    else if (n == "gemm.hint_a") o.gemm_hint_a = (v >= 0 && v <= 2) ? v : 0;
+    else if (n == "gemm.hint_b") o.gemm_hint_b = (v >= 0 && v <= 2) ? v : 0;
+    else if (n == "gemm.c_stream") o.gemm_c_stream = v ? 1 : 0;
+    else if (n == "gemm.peer_store") o.gemm_peer_store = v < 0 ? -1 : (v ? 1 : 0);
+    else if (n == "gemm.copy_ctas") { if (v > 128) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.copy_ctas is -1 (choose) or 0..128"); o.gemm_copy_ctas = v < 0 ? -1 : v; }
+    else if (n == "gemm.wait_limit_us") { if (value < 0 || value > 10000000) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.wait_limit_us is 0 (default) .. 10000000"); o.gemm_wait_limit_us = v; }
+    else if (n == "gemm.test_drop_commit") o.gemm_test_drop_commit = v ? 1 : 0;
+    else if (n == "gemm.verbose") o.gemm_verbose = v ? 1 : 0;
+    else if (n == "host_gemm.stage_chunks") { if (v < 0 || v > 256) return fail(ACCB_ERR_ARG, "accb_set_option: host_gemm.stage_chunks is 0 (default) .. 256"); o.host_stage_chunks = v; }
+    else return fail(ACCB_ERR_ARG, "accb_set_option: unknown option " + n);
     return ACCB_OK;
 }
 
@@ -422,8 +523,24 @@ int accb_gemm_replicated(const accb_gemm_desc* desc, const void* a, const void* 
     for (int r = 1; r < n_replicas; ++r) g.extra_c[r - 1] = c_replicas[r];
     g.stream = t_stream;
     g.status = sp->status;
+    g.launch_id = next_launch_id();
     g.device = dev;
     g.num_sms = sp->num_sms;
+    if (n_replicas > 1) {
+        // a region of the counter ring, large enough for any tiling of this problem (128 x 128 tiles at the least)
+        const int64_t need = ((d.m + 127) / 128) * ((d.n + 127) / 128);
+        std::lock_guard<std::mutex> lock(sp->mu);
+        if (!sp->tile_flags) {
+            cudaError_t e = cudaMalloc(&sp->tile_flags, kTileFlagInts * sizeof(int));
+            if (e != cudaSuccess) return fail_cuda("cudaMalloc(tile counters)", e);
+        }
+        if (need <= kTileFlagInts) {
+            if (sp->tile_flags_cursor + need > kTileFlagInts) sp->tile_flags_cursor = 0;
+            g.tile_flags = sp->tile_flags + sp->tile_flags_cursor;
+            g.tile_flags_capacity = need;
+            sp->tile_flags_cursor += need;
+        }
+    }
     const char* err = "";
     const int n = launch_gemm_umma(g, d.compute != ACCB_COMPUTE_TENSOR ? 1 : 0, &err);
     if (n < 0) return fail(n, std::string("accb_gemm_replicated: ") + err);
@@ -533,8 +650,9 @@ int accb_gather_rank2(const void* data, int64_t d0, int64_t d1, const int64_t* i
     if (dd != di || dd != dout) return fail(ACCB_ERR_ARG, "accb_gather_rank2: mix of host and device pointers");
     cudaStream_t stream = t_stream;
     const char* err = "";
+    const int launch_id = next_launch_id();
     if (dd) {
-        int n = launch_gather(data, d0, d1, indices, i0, i1, output, axis, elem_bytes, s.status, stream, &err);
+        int n = launch_gather(data, d0, d1, indices, i0, i1, output, axis, elem_bytes, s.status, launch_id, stream, &err);
         if (n < 0) return fail(n, std::string("accb_gather_rank2: ") + err);
         return ACCB_OK;
     }
@@ -546,11 +664,11 @@ int accb_gather_rank2(const void* data, int64_t d0, int64_t d1, const int64_t* i
     cudaError_t e = cudaMemcpyAsync(s.slot[0], data, bytes_data, cudaMemcpyHostToDevice, stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(s.slot[1], indices, bytes_idx, cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return fail_cuda("host to device copy", e);
-    int n = launch_gather(s.slot[0], d0, d1, (const int64_t*)s.slot[1], i0, i1, s.slot[2], axis, elem_bytes, s.status, stream, &err);
+    int n = launch_gather(s.slot[0], d0, d1, (const int64_t*)s.slot[1], i0, i1, s.slot[2], axis, elem_bytes, s.status, launch_id, stream, &err);
     if (n < 0) return fail(n, std::string("accb_gather_rank2: ") + err);
     e = cudaMemcpyAsync(output, s.slot[2], bytes_out, cudaMemcpyDeviceToHost, stream);
     if (e != cudaSuccess) return fail_cuda("device to host copy", e);
-    return collect_status(s, stream);
+    return collect_status(s, stream, COLLECT_GATHER, launch_id);
 }
 
 int64_t accb_range_count_f32(float start, float limit, float delta)
@@ -602,11 +720,34 @@ int accb_range_f32(int64_t n, float* output, float* start_inout, float delta)
 int accb_set_device(int32_t device)
 {
     t_error.clear();
+    if (device == -1) { t_device = -1; return ACCB_OK; }     // back to "whatever CUDA device is current"
     if (device < 0 || device >= kMaxDevices) return fail(ACCB_ERR_ARG, "accb_set_device: device index out of range");
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) return fail_cuda("cudaSetDevice", e);
     t_device = device;
     return ACCB_OK;
+}
+
+int accb_get_device(void) { return t_device; }
+
+int accb_current_device(void)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return ACCB_ERR_CUDA; }
+    return dev;
+}
+
+int accb_debug_decode_status(const int32_t* words, int32_t what, int32_t launch_id, char* message, int32_t capacity)
+{
+    if (!words) return ACCB_ERR_ARG;
+    int w[kStatusWords];
+    for (int i = 0; i < kStatusWords; ++i) w[i] = words[i];
+    bool cg = false, ca = false;
+    std::string msg;
+    const int rc = decode_status(w, what, launch_id, &cg, &ca, &msg);
+    if (message && capacity > 0) { strncpy(message, msg.c_str(), (size_t)capacity - 1); message[capacity - 1] = 0; }
+    return rc;
 }
 
 int accb_set_stream(void* cuda_stream)

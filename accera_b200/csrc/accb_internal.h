@@ -11,16 +11,43 @@
 
 namespace accb {
 
-// Words of the per-device status buffer that kernels write to (never trap):
-//   [0] gather: number of indices found outside [0, dim)
-//   [1] tcgen05 GEMM: first bounded wait that ran out, encoded as
-//       (site << 24) | (blockIdx.x & 0xffffff), 0 if none
-//   [2] tcgen05 GEMM: k-block / tile the wait was at
-//   [3] reserved
-constexpr int kStatusWords = 4;
+// Words of the per-device status buffer that kernels write to (never trap).  Every launch that can fail on the
+// device carries a launch id (next_launch_id), so that a failure is attributed to the launch that had it and a
+// stale, not yet collected failure of an earlier launch neither aborts nor mislabels a later one.
+//   [0] gather: number of indices found outside [0, dim) since the last collection
+//   [1] tcgen05 GEMM: first bounded wait that ran out, (site << 24) | (blockIdx.x & 0xffffff)
+//   [2] tcgen05 GEMM: k-block / tile that wait was at
+//   [3] tcgen05 GEMM: launch id of the launch that recorded [1] and [2]; 0 = no failure recorded
+//   [4] tcgen05 GEMM: number of waits that ran out since the last collection (all launches)
+//   [5] gather: launch id of the last launch that met a bad index
+constexpr int kStatusWords = 8;
+enum { ST_GATHER_COUNT = 0, ST_GEMM_SITE = 1, ST_GEMM_STEP = 2, ST_GEMM_ID = 3, ST_GEMM_COUNT = 4, ST_GATHER_ID = 5 };
 // The status buffer is followed by kPaceSlots counters: one per in-flight tensor-core GEMM launch,
 // used to keep its persistent CTAs roughly in step (see gemm_umma.cu).
 constexpr int kPaceSlots = 64;
+
+// a fresh non-zero launch id (process-wide, 31 bits, wraps past zero)
+int next_launch_id();
+
+// Per-thread overrides of what the launch code would choose by itself (accb_set_option): used by the tests to
+// reach every code path on small problems, by tuning runs, and by the time-out self-test.  Zero-initialised =
+// "choose as usual".
+struct Options {
+    int gemm_tile_cols = 0;          // 128 | 256: accumulator columns per tile
+    int gemm_staged_store = -1;      // 0: epilogue stores straight from registers, 1: shared-memory staging + TMA stores
+    int gemm_pace_pct = -1;          // tile-by-tile pacing of the persistent CTAs: 0 off, 1..100 on
+    int gemm_group_m = 0;            // tile rows visited together
+    int gemm_hint_a = 0, gemm_hint_b = 0;   // L2 eviction priority of the operand loads (1 evict-first, 2 evict-last)
+    int gemm_c_stream = 0;           // streaming (evict-first) accesses to C
+    int gemm_peer_store = -1;        // replicated GEMM: 0 = TMA stores to every replica, 1 = register stores to the peers
+    int gemm_copy_ctas = -1;         // replicated GEMM: CTAs that forward finished tiles to the replicas (0 = none: the
+                                     // computing CTAs' epilogues store to every replica themselves)
+    int gemm_wait_limit_us = 0;      // limit of every bounded device-side wait (default: one second)
+    int gemm_test_drop_commit = 0;   // self-test: the MMA issuer leaves out the commit that completes the last accumulator
+    int gemm_verbose = 0;            // print the launch plan to stderr
+    int host_stage_chunks = 0;       // row chunks of the staged host-pointer GEMM (default 16)
+};
+Options& options();
 
 struct GemmLaunch {
     accb_gemm_desc d;
@@ -32,12 +59,17 @@ struct GemmLaunch {
     // only the tensor-core path with a TMA-storable C supports them
     void* extra_c[7];
     int n_extra_c;
+    // per-tile completion counters for a replicated launch with forwarding CTAs (device memory, this launch's own
+    // region; the launch code zeroes what it uses), null = not available
+    int* tile_flags = nullptr;
+    int64_t tile_flags_capacity = 0;
     // batched GEMM: `batch` independent problems of the same shape; operand i of problem b starts
     // b * *_batch_stride elements after the base (a stride of 0 shares that operand between all problems)
     int64_t batch = 1;
     int64_t a_batch_stride = 0, b_batch_stride = 0, c_batch_stride = 0;
     cudaStream_t stream;
     int* status;       // device pointer to kStatusWords ints
+    int launch_id;     // attribution of device-side failures (next_launch_id)
     int device;
     int num_sms;
 };
@@ -51,6 +83,9 @@ bool gemm_umma_supported(const GemmLaunch& g, const char** why);
 int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err);
 // host only: the tile shape launch_gemm_umma would pick (from d, batch, num_sms, max_ctas) and the rounds of tiles it gives
 void gemm_umma_tile_plan(const GemmLaunch& g, int want_two_sm, int* two_sm, int* tile_cols, int64_t* tiles, int64_t* rounds);
+// host only: grid, block and dynamic shared memory of the launch launch_gemm_umma would make (out[0..2] grid,
+// out[3..5] block, out[6] dynamic shared-memory bytes, out[7] pipeline stages)
+void gemm_umma_launch_geometry(const GemmLaunch& g, int want_two_sm, int32_t out[8]);
 
 // reduce_mean.cu
 // Scratch (fp32 partial sums) a launch needs for these dims, in bytes; 0 when the
@@ -61,7 +96,7 @@ int launch_reduce_mean(const float* data, int64_t d0, int64_t d1, int64_t d2, fl
 
 // gather.cu
 int launch_gather(const void* data, int64_t d0, int64_t d1, const int64_t* indices, int64_t i0, int64_t i1,
-                  void* output, int axis, int elem_bytes, int* status, cudaStream_t stream, const char** err);
+                  void* output, int axis, int elem_bytes, int* status, int launch_id, cudaStream_t stream, const char** err);
 
 // range.cu: output[i] = start + i rounded additions of delta (bit-identical to the serial recurrence); writes the
 // value after n additions to *final_value (host memory).  range_count_f32 is host-only.
@@ -76,5 +111,10 @@ void note_launches(int n);
 
 // records `msg` as the calling thread's last error (what accb_last_error returns) and returns `code`
 int set_error(int code, const char* msg);
+// forgets the calling thread's last error (every entry point starts with this)
+void clear_error();
+// the device this thread's calls run on: the one chosen with accb_set_device (made current here), else the current
+// CUDA device.  Returns ACCB_OK or an error code (with the error text recorded).
+int selected_device(int* dev);
 
 }  // namespace accb

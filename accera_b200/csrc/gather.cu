@@ -24,13 +24,13 @@ constexpr int kUnroll = 4;
 __global__ void __launch_bounds__(kBlock)
 gather_rows_vec_kernel(const uint4* __restrict__ data, const int64_t* __restrict__ indices,
                        uint4* __restrict__ output, int64_t n_rows_in, int64_t vec_per_row,
-                       int64_t chunks_per_row, int* __restrict__ status)
+                       int64_t chunks_per_row, int* __restrict__ status, int launch_id)
 {
     const int64_t row = blockIdx.x / chunks_per_row;
     const int64_t chunk = blockIdx.x % chunks_per_row;
     const int64_t src_row = indices[row];
     const bool ok = (src_row >= 0) && (src_row < n_rows_in);
-    if (!ok && threadIdx.x == 0 && chunk == 0) atomicAdd(status, 1);
+    if (!ok && threadIdx.x == 0 && chunk == 0) { atomicAdd(status + ST_GATHER_COUNT, 1); status[ST_GATHER_ID] = launch_id; }
     const uint4* src = data + (ok ? src_row : 0) * vec_per_row;
     uint4* dst = output + row * vec_per_row;
     const int64_t v0 = chunk * (kBlock * kUnroll) + threadIdx.x;
@@ -53,7 +53,7 @@ gather_rows_vec_kernel(const uint4* __restrict__ data, const int64_t* __restrict
 template <typename T>
 __global__ void __launch_bounds__(kBlock)
 gather_elem_kernel(const T* __restrict__ data, const int64_t* __restrict__ indices, T* __restrict__ output,
-                   int64_t d0, int64_t d1, int64_t n_idx, int axis, int64_t total, int* __restrict__ status)
+                   int64_t d0, int64_t d1, int64_t n_idx, int axis, int64_t total, int* __restrict__ status, int launch_id)
 {
     for (int64_t e = (int64_t)blockIdx.x * kBlock + threadIdx.x; e < total; e += (int64_t)gridDim.x * kBlock) {
         int64_t src;
@@ -63,13 +63,13 @@ gather_elem_kernel(const T* __restrict__ data, const int64_t* __restrict__ indic
             const int64_t ix = indices[row];
             ok = (ix >= 0) && (ix < d0);
             src = ix * d1 + k;
-            if (!ok && k == 0) atomicAdd(status, 1);
+            if (!ok && k == 0) { atomicAdd(status + ST_GATHER_COUNT, 1); status[ST_GATHER_ID] = launch_id; }
         } else {
             const int64_t i = e / n_idx, jk = e - i * n_idx;
             const int64_t ix = indices[jk];
             ok = (ix >= 0) && (ix < d1);
             src = i * d1 + ix;
-            if (!ok && i == 0) atomicAdd(status, 1);
+            if (!ok && i == 0) { atomicAdd(status + ST_GATHER_COUNT, 1); status[ST_GATHER_ID] = launch_id; }
         }
         output[e] = ok ? __ldg(data + src) : T(0);
     }
@@ -77,19 +77,19 @@ gather_elem_kernel(const T* __restrict__ data, const int64_t* __restrict__ indic
 
 template <typename T>
 cudaError_t launch_elem(const void* data, const int64_t* indices, void* output, int64_t d0, int64_t d1, int64_t n_idx,
-                        int axis, int64_t total, int* status, cudaStream_t stream)
+                        int axis, int64_t total, int* status, int launch_id, cudaStream_t stream)
 {
     int64_t blocks = (total + kBlock - 1) / kBlock;
     if (blocks > 148 * 64) blocks = 148 * 64;   // grid-stride beyond this
     gather_elem_kernel<T><<<(unsigned)blocks, kBlock, 0, stream>>>((const T*)data, indices, (T*)output, d0, d1, n_idx,
-                                                                  axis, total, status);
+                                                                  axis, total, status, launch_id);
     return cudaGetLastError();
 }
 
 }  // namespace
 
 int launch_gather(const void* data, int64_t d0, int64_t d1, const int64_t* indices, int64_t i0, int64_t i1,
-                  void* output, int axis, int elem_bytes, int* status, cudaStream_t stream, const char** err)
+                  void* output, int axis, int elem_bytes, int* status, int launch_id, cudaStream_t stream, const char** err)
 {
     const int64_t n_idx = i0 * i1;
     const int64_t total = (axis == 0) ? n_idx * d1 : d0 * n_idx;
@@ -103,14 +103,14 @@ int launch_gather(const void* data, int64_t d0, int64_t d1, const int64_t* indic
         const int64_t cpr = (vpr + kBlock * kUnroll - 1) / (kBlock * kUnroll);
         if (n_idx * cpr > 0x7fffffff) { *err = "gather: too many rows for this kernel's grid"; return ACCB_ERR_ARG; }
         gather_rows_vec_kernel<<<(unsigned)(n_idx * cpr), kBlock, 0, stream>>>(
-            (const uint4*)data, indices, (uint4*)output, d0, vpr, cpr, status);
+            (const uint4*)data, indices, (uint4*)output, d0, vpr, cpr, status, launch_id);
         e = cudaGetLastError();
     } else {
         switch (elem_bytes) {
-        case 1: e = launch_elem<uint8_t>(data, indices, output, d0, d1, n_idx, axis, total, status, stream); break;
-        case 2: e = launch_elem<uint16_t>(data, indices, output, d0, d1, n_idx, axis, total, status, stream); break;
-        case 4: e = launch_elem<uint32_t>(data, indices, output, d0, d1, n_idx, axis, total, status, stream); break;
-        case 8: e = launch_elem<uint64_t>(data, indices, output, d0, d1, n_idx, axis, total, status, stream); break;
+        case 1: e = launch_elem<uint8_t>(data, indices, output, d0, d1, n_idx, axis, total, status, launch_id, stream); break;
+        case 2: e = launch_elem<uint16_t>(data, indices, output, d0, d1, n_idx, axis, total, status, launch_id, stream); break;
+        case 4: e = launch_elem<uint32_t>(data, indices, output, d0, d1, n_idx, axis, total, status, launch_id, stream); break;
+        case 8: e = launch_elem<uint64_t>(data, indices, output, d0, d1, n_idx, axis, total, status, launch_id, stream); break;
         default: *err = "gather: elem_bytes must be 1, 2, 4 or 8"; return ACCB_ERR_ARG;
         }
     }

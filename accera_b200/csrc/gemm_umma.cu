@@ -60,7 +60,7 @@ constexpr uint32_t kPeerMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a sha
 enum { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2 };
 
 // where a bounded wait gave up (status word 1, bits 31..24)
-enum { SITE_PRODUCER_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_TMEM_EMPTY = 3, SITE_EPI_TMEM_FULL = 4 };
+enum { SITE_PRODUCER_EMPTY = 1, SITE_MMA_FULL = 2, SITE_MMA_TMEM_EMPTY = 3, SITE_EPI_TMEM_FULL = 4, SITE_COPY_TILE = 5 };
 
 // BN = accumulator columns per tile: 256, or 128 for problems whose tile count fills the SMs badly at 256
 template <bool TWO_SM, int BN> struct SmemPlan {
@@ -79,6 +79,7 @@ template <bool TWO_SM, int BN> struct SmemPlan {
 };
 
 constexpr int kMaxReplicas = 8;
+constexpr int kPeerStoreDefault = 0;   // how replicas in peer memory are written unless overridden: 0 TMA stores, 1 register stores
 struct CReplicaMaps { CUtensorMap m[kMaxReplicas]; };   // tensor maps of the C replicas (TMA-store epilogue)
 
 struct UmmaParams {
@@ -105,7 +106,17 @@ struct UmmaParams {
     int batch;
     int a_batched, b_batched;
     int64_t c_bs;
-    int verbose;            // host only: print the launch plan to stderr (tuning override v=1)
+    int verbose;            // host only: print the launch plan to stderr
+    int launch_id;          // non-zero id of this launch: failures recorded in the status buffer carry it
+    unsigned long long wait_ns;   // limit of every bounded wait, in nanoseconds of the global timer
+    int drop_commit;        // self-test of the time-out path: the commit completing each CTA's last accumulator is left out
+    int peer_store;         // replicas 1.. are written with 16-byte register stores read back from the staging box
+                            // (replica 0 keeps its TMA store); 0 = one TMA store per replica
+    void* peer_c[kMaxReplicas - 1];   // base pointers of replicas 1.. (peer_store and copy CTAs)
+    int copy_ctas;          // > 0: the last copy_ctas CTAs of the grid compute nothing; they forward every finished tile
+                            // of the local C to the replicas (see copy_tiles).  The computing CTAs then store to C only.
+    int* tile_flags;        // copy_ctas > 0: one counter per tile, bumped by every epilogue warp once its part of the
+                            // tile is in C; zeroed by the host before the launch
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -136,26 +147,40 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 
-// Bounded wait.  Returns false when it gave up (after about a second, or as soon
-// as any CTA of the grid has recorded a failure), having recorded the site.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* status, int site, int detail)
+__device__ __forceinline__ unsigned long long global_timer_ns()
 {
-    const long long t0 = clock64();
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait.  Returns false when it gave up: after `wait_ns` (a second unless the caller asked otherwise), or as
+// soon as a CTA of THIS launch has recorded a failure.  The first failure of a launch is recorded with the launch's
+// id; a record left by an earlier launch is not this launch's business and neither stops it nor is overwritten.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* status, int launch_id, unsigned long long wait_ns,
+                                            int site, int detail)
+{
+    const unsigned long long t0 = global_timer_ns();
     for (uint32_t spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 0xff) == 0xff) {
-            if (*(volatile int*)(status + 1) != 0) return false;   // someone else already failed
-            if (clock64() - t0 > 2000000000LL) {
-                if (atomicCAS(status + 1, 0, (site << 24) | (int)(blockIdx.x & 0xffffff)) == 0) status[2] = detail;
+        if ((spin & 0x3f) == 0x3f) {
+            if (*(volatile int*)(status + ST_GEMM_ID) == launch_id) return false;   // another CTA of this launch already failed
+            if (global_timer_ns() - t0 > wait_ns) {
+                atomicAdd(status + ST_GEMM_COUNT, 1);
+                if (atomicCAS(status + ST_GEMM_ID, 0, launch_id) == 0) {
+                    status[ST_GEMM_SITE] = (site << 24) | (int)(blockIdx.x & 0xffffff);
+                    status[ST_GEMM_STEP] = detail;
+                }
                 return false;
             }
         }
     }
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int site, int detail)
+struct WaitCtx { int* status; int launch_id; unsigned long long wait_ns; };
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, int site, int detail)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, status, site, detail);
+    return mbar_wait_slow(bar, parity, w.status, w.launch_id, w.wait_ns, site, detail);
 }
 
 // L2 eviction-priority policy for the operand loads; 0 = none (the plain load form is used)
@@ -619,6 +644,149 @@ __device__ __forceinline__ void issue_stage(uint32_t tmem_d, uint32_t sa, uint32
                            idesc, (!first_kb || j > 0) ? 1u : 0u);
 }
 
+// The forwarding role of a replicated GEMM: CTAs that own no tensor-core work.  Copy CTA `copy_rank` of `n_copy`
+// takes tiles copy_rank, copy_rank + n_copy, ... (the order in which the computing CTAs finish them) and moves
+// each one, in bands of 32 rows, from the local C to every replica:
+//   thread 0        waits until all epilogue warps of the tile have landed their part in C (a counter per tile,
+//                   release / acquire), then TMA-loads the tile's bands from C (L2) into a ring of shared-memory
+//                   slots, running up to a whole ring ahead of the stores
+//   warps 1 .. 5    take the slots in order, read each band out of shared memory 16 bytes per thread and write
+//                   it to every replica with plain stores (all of a thread's loads first, then the stores)
+// Stores issued by the load/store units keep far more bytes in flight per SM than TMA stores do (measured per
+// forwarding CTA with one peer: 16 GB/s with TMA stores, limited by the round trip over NVLink).
+//
+// Why separate CTAs: a store to another GPU waits for NVLink, and while it waits it holds up everything queued
+// behind it on its SM's way out - including the operand fetches of that SM's MMA pipeline.  Measured on two
+// B200s with the 8-GPU traffic pattern (7 x 128 MiB out and in per GPU, 8192^3 bf16 per step, sustained):
+// stores issued by the computing CTAs' epilogues 1.55 ms per step, the same bytes stored from 16 SMs of their
+// own next to a GEMM on 132 SMs 1.40 ms (the link alone needs 1.39); stores issued from the computing SMs by
+// co-resident CTAs 2.03 ms.
+template <typename TC, bool TWO_SM, int BN>
+__device__ void copy_tiles(const UmmaParams& p, const CReplicaMaps& cmaps, uint32_t smem_base, uint8_t* smem_gen,
+                           int copy_rank, int n_copy)
+{
+    constexpr int kRows = TWO_SM ? 2 * kBlockM : kBlockM;
+    constexpr int kBoxCols = 128 / (int)sizeof(TC);              // elements per 128-byte box row
+    constexpr int kBoxes = BN / kBoxCols;                        // boxes per band (32 rows x BN columns)
+    constexpr uint32_t kBoxBytes = 32 * 128;
+    constexpr uint32_t kSlotBytes = kBoxes * kBoxBytes;          // 16 KB (2-byte C, 256 columns) .. 32 KB
+    constexpr int kSlots = (192 * 1024) / (int)kSlotBytes;       // 12 .. 6
+    constexpr int kStoreWarps = kThreads / 32 - 1;
+    constexpr int kStoreThreads = kStoreWarps * 32;
+    constexpr int kVecPerBand = 32 * kBoxes * 8;                 // 16-byte vectors in a band
+    constexpr int kVecPerThread = (kVecPerBand + kStoreThreads - 1) / kStoreThreads;
+    constexpr int kPerVec = 16 / (int)sizeof(TC);
+    struct BandMeta { int col, row, boxes, pad; };               // boxes < 0: no more bands
+    const uint32_t bars = smem_base + (uint32_t)kSlots * kSlotBytes;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (kSlots + s); };
+    volatile BandMeta* meta = reinterpret_cast<volatile BandMeta*>(smem_gen + (size_t)kSlots * kSlotBytes + 16 * kSlots);
+    const WaitCtx wctx{p.status, p.launch_id, p.wait_ns};
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kSlots; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), kStoreWarps); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 0) {
+        if (lane != 0) return;
+        // ---------------- loader ----------------
+        const int num_tiles = p.tiles_m * p.tiles_n;
+        const int expected = kEpiWarps * (TWO_SM ? 2 : 1);
+        long long issued = 0;
+        bool ok = true;
+        for (int t = copy_rank; t < num_tiles && ok; t += n_copy) {
+            // bounded wait for the tile (it may legitimately take most of the launch to appear)
+            const unsigned long long t0 = global_timer_ns();
+            for (uint32_t spin = 0;; ++spin) {
+                int have;
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(have) : "l"(p.tile_flags + t) : "memory");
+                if (have >= expected) break;
+                __nanosleep(100);
+                if ((spin & 0x3f) == 0x3f) {
+                    if (*(volatile int*)(p.status + ST_GEMM_ID) == p.launch_id) { ok = false; break; }
+                    if (global_timer_ns() - t0 > p.wait_ns) {
+                        atomicAdd(p.status + ST_GEMM_COUNT, 1);
+                        if (atomicCAS(p.status + ST_GEMM_ID, 0, p.launch_id) == 0) {
+                            p.status[ST_GEMM_SITE] = (SITE_COPY_TILE << 24) | (int)(blockIdx.x & 0xffffff);
+                            p.status[ST_GEMM_STEP] = t;
+                        }
+                        ok = false;
+                        break;
+                    }
+                }
+            }
+            if (!ok) break;
+            // the tile was written through the async proxy and is read through it: order those reads after the acquire
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            int tm, tn;
+            tile_coords(t, p, tm, tn);
+            const int64_t row0 = (int64_t)tm * kRows;
+            const int col0 = tn * BN;
+            const int bands = (int)((min((int64_t)kRows, p.m - row0) + 31) / 32);
+            const int nb = (int)min((int64_t)kBoxes, (p.n - col0 + kBoxCols - 1) / kBoxCols);   // boxes that touch the matrix
+            for (int band = 0; band < bands; ++band, ++issued) {
+                const int slot = (int)(issued % kSlots);
+                if (issued >= kSlots && !mbar_wait(empty_bar(slot), (uint32_t)(((issued / kSlots) - 1) & 1), wctx, SITE_COPY_TILE, t)) { ok = false; break; }
+                meta[slot].col = col0;
+                meta[slot].row = (int)(row0 + band * 32);
+                meta[slot].boxes = nb;
+                const uint32_t dst = smem_base + (uint32_t)slot * kSlotBytes;
+                mbar_arrive_expect_tx(full_bar(slot), (uint32_t)nb * kBoxBytes);   // a box clipped by the matrix edge still arrives whole
+#pragma unroll
+                for (int b = 0; b < kBoxes; ++b)
+                    if (b < nb) tma_load_2d(dst + b * kBoxBytes, &cmaps.m[0], full_bar(slot), col0 + b * kBoxCols, (int)(row0 + band * 32), 0);
+            }
+        }
+        // end marker for the storing warps (also after a failure, so that they leave)
+        {
+            const int slot = (int)(issued % kSlots);
+            bool free_slot = true;
+            if (issued >= kSlots && ok) free_slot = mbar_wait(empty_bar(slot), (uint32_t)(((issued / kSlots) - 1) & 1), wctx, SITE_COPY_TILE, -1);
+            if (free_slot || !ok) {
+                meta[slot].boxes = -1;
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(full_bar(slot)) : "memory");
+            }
+        }
+        // loads still in flight after a failure: give them time to land before shared memory is released
+        if (!ok) for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    } else {
+        // ---------------- storing warps ----------------
+        const int tid = (int)threadIdx.x - 32;
+        const int64_t pitch = p.cs0 * (int64_t)sizeof(TC);
+        for (long long j = 0;; ++j) {
+            const int slot = (int)(j % kSlots);
+            if (!__all_sync(0xffffffffu, mbar_wait(full_bar(slot), (uint32_t)((j / kSlots) & 1), wctx, SITE_COPY_TILE, -2))) break;
+            const int nb = meta[slot].boxes;
+            if (nb < 0) break;
+            const int col = meta[slot].col, row = meta[slot].row;
+            const uint8_t* src = smem_gen + (size_t)slot * kSlotBytes;
+            uint4 v[kVecPerThread];
+            int64_t off[kVecPerThread];
+            const int total = 32 * nb * 8;
+#pragma unroll
+            for (int i = 0; i < kVecPerThread; ++i) {
+                // vector -> (box, row in band, 16-byte unit): 8 consecutive threads cover one 128-byte box row
+                const int vi = tid + i * kStoreThreads;
+                const int b = vi >> 8, r = (vi >> 3) & 31, u = vi & 7;
+                const int64_t c = (int64_t)col + b * kBoxCols + u * kPerVec;
+                const bool live = vi < total && row + r < p.m && c + kPerVec <= p.n;
+                off[i] = live ? (int64_t)(row + r) * pitch + c * (int64_t)sizeof(TC) : -1;
+                if (live) v[i] = *reinterpret_cast<const uint4*>(src + b * kBoxBytes + r * 128 + ((u ^ (r & 7)) << 4));
+            }
+            for (int rep = 0; rep < p.n_replicas - 1; ++rep) {
+                char* dst = reinterpret_cast<char*>(p.peer_c[rep]);
+#pragma unroll
+                for (int i = 0; i < kVecPerThread; ++i)
+                    if (off[i] >= 0) *reinterpret_cast<uint4*>(dst + off[i]) = v[i];
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar(slot)) : "memory");
+        }
+    }
+}
+
 template <int KIND, typename TC, bool TWO_SM, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -648,8 +816,16 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const WaitCtx wctx{p.status, p.launch_id, p.wait_ns};
     const uint32_t rank = TWO_SM ? cluster_ctarank() : 0u;
     const bool leader = (rank == 0);
+
+    // replicated GEMM with forwarding CTAs: the last copy_ctas CTAs (whole clusters) only move finished tiles
+    const int compute_ctas = (int)gridDim.x - p.copy_ctas;
+    if ((int)blockIdx.x >= compute_ctas) {
+        copy_tiles<TC, TWO_SM, BN>(p, cmaps, smem_base, smem_gen, (int)blockIdx.x - compute_ctas, p.copy_ctas);
+        return;
+    }
 
     auto record_give_up = [&]() {
         gave_up[rank] = 1u;
@@ -691,7 +867,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t tmem_base = *tmem_holder;
 
     const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
-    const int num_units = (int)gridDim.x / kCtas;
+    const int num_units = compute_ctas / kCtas;
     const int unit = (int)blockIdx.x / kCtas;
     constexpr int slab_elems = kSlabBytes / ElemBytes<KIND>::value;
     const int num_kb = (int)((p.k + slab_elems - 1) / slab_elems);
@@ -734,7 +910,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         if (!in_time) pacing = false;      // the other CTAs are not running alongside: stop waiting for them
                     }
                     for (int kb = 0; kb < num_kb; ++kb) {
-                        if (!mbar_wait(empty_bar(s), ph ^ 1u, p.status, SITE_PRODUCER_EMPTY, kb)) { ok = false; break; }
+                        if (!mbar_wait(empty_bar(s), ph ^ 1u, wctx, SITE_PRODUCER_EMPTY, kb)) { ok = false; break; }
                         const uint32_t sa = smem_base + s * Plan::kStageBytes;
                         const uint32_t sb = sa + Plan::kABytes;
                         if constexpr (TWO_SM) {
@@ -781,11 +957,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 for (int t = unit; t < num_tiles && ok; t += num_units, ++local) {
                     const int buf = local & 1;
                     const uint32_t tph = (local >> 1) & 1u;
-                    if (!mbar_wait(tmem_empty_bar(buf), tph ^ 1u, p.status, SITE_MMA_TMEM_EMPTY, local)) { ok = false; break; }
+                    if (!mbar_wait(tmem_empty_bar(buf), tph ^ 1u, wctx, SITE_MMA_TMEM_EMPTY, local)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
                     for (int kb = 0; kb < num_kb; ++kb) {
-                        if (!mbar_wait(full_bar(s), ph, p.status, SITE_MMA_FULL, kb)) { ok = false; break; }
+                        if (!mbar_wait(full_bar(s), ph, wctx, SITE_MMA_FULL, kb)) { ok = false; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint32_t sa = smem_base + s * Plan::kStageBytes;
                         const uint32_t sb = sa + Plan::kABytes;
@@ -793,7 +969,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         umma_commit<TWO_SM>(empty_bar(s));            // frees the stage once these MMAs have read it
                         if (++s == S) { s = 0; ph ^= 1u; }
                     }
-                    if (ok) umma_commit<TWO_SM>(tmem_full_bar(buf));  // accumulator complete
+                    // accumulator complete (the time-out self-test leaves out the one that completes this CTA's last tile:
+                    // its MMAs still finish, but nothing tells the epilogue, whose bounded wait then runs out)
+                    if (ok && !(p.drop_commit && t + num_units >= num_tiles)) umma_commit<TWO_SM>(tmem_full_bar(buf));
                 }
                 if (!ok) record_give_up();
             };
@@ -817,7 +995,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const int buf = local & 1;
             const uint32_t tph = (local >> 1) & 1u;
             // all 32 lanes must agree before the warp-wide TMEM loads below
-            if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), tph, p.status, SITE_EPI_TMEM_FULL, local))) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), tph, wctx, SITE_EPI_TMEM_FULL, local))) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int64_t row = (int64_t)(tm * kCtas + (int)rank) * kBlockM + q * 32 + lane;
             const int64_t col_tile = (int64_t)tn * BN;
@@ -857,8 +1035,33 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         __syncwarp();
                         if (lane == 0) {
                             const uint32_t src = smem_u32(box);
-                            for (int r = 0; r < p.n_replicas; ++r) tma_store_2d(&cmaps.m[r], src, (int)box_col0, (int)row0);
+                            const int n_tma = (p.peer_store || p.copy_ctas > 0) ? 1 : p.n_replicas;
+                            for (int r = 0; r < n_tma; ++r) tma_store_2d(&cmaps.m[r], src, (int)box_col0, (int)row0);
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                        if (p.peer_store && p.copy_ctas == 0 && p.n_replicas > 1) {
+                            // Replicas in other GPUs' memory: the warp reads the box back, 16 bytes per lane (8 lanes
+                            // cover one 128-byte row, a step covers 4 rows), and writes it to every peer with plain
+                            // stores.  A TMA store that waits for NVLink holds up the operand loads queued behind it in
+                            // the same TMA unit; these stores wait in the load/store path instead.
+                            const int u = lane & 7, r4 = lane >> 3;
+                            constexpr int kPerVec = 16 / (int)sizeof(TC);
+                            const int64_t colu = box_col0 + (int64_t)u * kPerVec;
+                            const bool col_ok = colu + kPerVec <= p.n;
+                            uint4 v[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int r = 4 * i + r4;
+                                v[i] = *reinterpret_cast<const uint4*>(box + r * 128 + ((u ^ (r & 7)) << 4));
+                            }
+                            const int64_t row_step = 4 * p.cs0 * (int64_t)sizeof(TC);
+                            for (int rep = 1; rep < p.n_replicas; ++rep) {
+                                char* dst = reinterpret_cast<char*>(p.peer_c[rep - 1]) +
+                                            ((row0 + r4) * p.cs0 + colu) * (int64_t)sizeof(TC);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    if (col_ok && row0 + 4 * i + r4 < p.m) *reinterpret_cast<uint4*>(dst + i * row_step) = v[i];
+                            }
                         }
                         ++store_count;
                     }
@@ -868,12 +1071,20 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(TWO_SM ? (tmem_empty_bar(buf) & kPeerMask) : tmem_empty_bar(buf));
+            if (p.copy_ctas > 0 && lane == 0) {
+                // this warp's part of the tile is on its way to C: once the stores have completed, publish it to
+                // the forwarding CTAs (TMA writes belong to the async proxy, the readers use ordinary loads)
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+                __threadfence();
+                asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.tile_flags + t) : "memory");
+            }
         }
         if (!ok && lane == 0) record_give_up();
         // Before the CTA exits its TMA stores must at least have read their shared-memory boxes; the global writes
         // themselves are complete when the grid is.  Stores into other GPUs' memory are waited for in full.
         if (lane == 0) {
-            if (p.n_replicas > 1) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            if (p.n_replicas > 1 && p.copy_ctas == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
             else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         }
         __syncwarp();
@@ -1044,12 +1255,20 @@ int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap
         const int cap = g.d.max_ctas / (TWO_SM ? 2 : 1);
         if (cap >= 1 && cap < units) units = cap;
     }
+    // forwarding CTAs take whole units (clusters) out of the resident set; the rest compute
+    const int copy_units = p.copy_ctas / (TWO_SM ? 2 : 1);
+    if (copy_units > 0) {
+        if (units - copy_units < 1) { *err = "tcgen05 GEMM: no SM left for computing beside the forwarding CTAs"; return ACCB_ERR_ARG; }
+        units -= copy_units;
+    }
     if (units > num_tiles) units = num_tiles;
     if (p.verbose)
         fprintf(stderr, "tcgen05 GEMM %lld x %lld x %lld x %d: %s tiles of %d columns, %d tiles on %d %s, pacing %d%%\n",
                 (long long)p.m, (long long)p.n, (long long)p.k, p.batch, TWO_SM ? "pair" : "single-CTA", BN, num_tiles, units,
                 TWO_SM ? "pairs" : "CTAs", p.pace_pct);
-    cfg.gridDim = dim3((unsigned)(units * (TWO_SM ? 2 : 1)));
+    if (p.verbose && p.n_replicas > 1)
+        fprintf(stderr, "  %d replicas: %s\n", p.n_replicas, p.copy_ctas > 0 ? "forwarding CTAs" : p.peer_store ? "register stores from the epilogue" : "TMA stores from the epilogue");
+    cfg.gridDim = dim3((unsigned)((units + copy_units) * (TWO_SM ? 2 : 1)));
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ma, mb, cm, (TC*)g.c, g.bias, p);
     if (e != cudaSuccess) { *err = cudaGetErrorString(e); return ACCB_ERR_CUDA; }
     note_launches(1);
@@ -1072,10 +1291,7 @@ TileChoice choose_tile(const GemmLaunch& g, int want_two_sm /* -1: free, 0 / 1: 
     // 1518 / 1346 / 972 / 851 TFLOP/s at 8192^3).  128-column tiles need 1.5x the L2 -> shared-memory traffic
     // per flop and are bound by it; they only pay on problems too small to give every SM a 256-column tile.
     static const double kEff[2][2] = { /* 1 SM */ { 0.64 /*128*/, 0.89 /*256*/ }, /* pair */ { 0.56 /*128*/, 1.00 /*256*/ } };
-    int force_bn = 0;
-    if (const char* tune = getenv("ACCB_GEMM_TUNE"))
-        for (const char* q = tune; *q; ++q)
-            if (q[0] == 'n' && q[1] == '=') force_bn = atoi(q + 2);
+    const int force_bn = options().gemm_tile_cols;
     TileChoice best{want_two_sm != 0, kBlockN};
     double best_cost = -1.0;
     for (int two = 1; two >= 0; --two) {
@@ -1113,6 +1329,31 @@ void gemm_umma_tile_plan(const GemmLaunch& g, int want_two_sm, int* two_sm, int*
     *tile_cols = t.bn;
     *tiles = n_tiles;
     *rounds = (n_tiles + units - 1) / units;
+}
+
+void gemm_umma_launch_geometry(const GemmLaunch& g, int want_two_sm, int32_t out[8])
+{
+    const TileChoice t = choose_tile(g, want_two_sm);
+    const int64_t rows = t.two_sm ? 2 * kBlockM : kBlockM;
+    const int64_t batch = g.batch > 1 ? g.batch : 1;
+    const int64_t n_tiles = ((g.d.m + rows - 1) / rows) * ((g.d.n + t.bn - 1) / t.bn) * batch;
+    const int per = t.two_sm ? 2 : 1;
+    int64_t units = g.num_sms / per;
+    if (g.d.max_ctas > 0 && g.d.max_ctas / per >= 1 && g.d.max_ctas / per < units) units = g.d.max_ctas / per;
+    if (units > n_tiles) units = n_tiles;
+    if (units < 1) units = 1;
+    int smem = 0, stages = 0;
+    if (t.two_sm) {
+        if (t.bn == 256) { smem = SmemPlan<true, 256>::kTotal; stages = SmemPlan<true, 256>::kStages; }
+        else { smem = SmemPlan<true, 128>::kTotal; stages = SmemPlan<true, 128>::kStages; }
+    } else {
+        if (t.bn == 256) { smem = SmemPlan<false, 256>::kTotal; stages = SmemPlan<false, 256>::kStages; }
+        else { smem = SmemPlan<false, 128>::kTotal; stages = SmemPlan<false, 128>::kStages; }
+    }
+    out[0] = (int32_t)(units * per); out[1] = 1; out[2] = 1;
+    out[3] = kThreads; out[4] = 1; out[5] = 1;
+    out[6] = smem;
+    out[7] = stages;
 }
 
 bool gemm_umma_supported(const GemmLaunch& g, const char** why)
@@ -1186,8 +1427,6 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
     p.c_bs = batch > 1 ? g.c_batch_stride : 0;
     const int64_t tiles_total = (int64_t)p.tiles_m * p.tiles_n * batch;
     const int64_t units_est = two_sm ? g.num_sms / 2 : g.num_sms;
-    p.hint_a = 0; p.hint_b = 0; p.c_stream = 0;
-    p.verbose = 0;
     // Epilogue path: staged TMA stores whenever C allows it.  Storing straight from registers looked 2 - 3 us
     // faster for one-round problems when each launch was timed cold under a profiler, but is equal or slower
     // (4096 x 768 x 3072: 784 vs 852 TFLOP/s) in a warm launch sequence.  Batched problems use plain stores.
@@ -1199,18 +1438,37 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
     p.pace_pct = (tiles_total >= 8 * units_est) ? 100 : 0;
     if (p.pace_pct && two_sm && p.tiles_m >= 32) p.group_m = 16;
     p.pace = g.status + kStatusWords;
-    if (const char* tune = getenv("ACCB_GEMM_TUNE")) {
-        // tuning override for experiments: "g=<group_m>,a=<0|1|2>,b=<0|1|2>,c=<0|1>,t=<0|1>,s=<pace %>,n=<128|256>,v=<0|1 print the plan>"
-        for (const char* q = tune; *q; ++q) {
-            if (q[1] != '=') continue;
-            const int v = atoi(q + 2);
-            if (*q == 'g' && v > 0) p.group_m = v;
-            else if (*q == 'a') p.hint_a = v;
-            else if (*q == 'b') p.hint_b = v;
-            else if (*q == 'c') p.c_stream = v;
-            else if (*q == 't' && g.n_extra_c == 0) p.tma_store = (v && c_tma_storable(d, g.c) && batch == 1) ? 1 : 0;
-            else if (*q == 's') p.pace_pct = v;
-            else if (*q == 'v') p.verbose = v;
+    {
+        // per-thread overrides (accb_set_option): tests reach every path on small problems with them
+        const Options& o = options();
+        if (o.gemm_group_m > 0) p.group_m = o.gemm_group_m;
+        p.hint_a = o.gemm_hint_a; p.hint_b = o.gemm_hint_b; p.c_stream = o.gemm_c_stream;
+        if (o.gemm_staged_store >= 0 && g.n_extra_c == 0) p.tma_store = (o.gemm_staged_store && c_tma_storable(d, g.c) && batch == 1) ? 1 : 0;
+        if (o.gemm_pace_pct >= 0) p.pace_pct = o.gemm_pace_pct;
+        p.verbose = o.gemm_verbose;
+        p.wait_ns = o.gemm_wait_limit_us > 0 ? (unsigned long long)o.gemm_wait_limit_us * 1000ull : 1000000000ull;
+        p.drop_commit = o.gemm_test_drop_commit ? 1 : 0;
+        // peers are written with register stores unless the caller asks for TMA stores or a row's last vector is partial
+        const bool vec_rows = ((d.n * elem_size(d.c_type)) % 16) == 0;
+        p.peer_store = (g.n_extra_c > 0 && vec_rows && (o.gemm_peer_store < 0 ? kPeerStoreDefault : o.gemm_peer_store)) ? 1 : 0;
+    }
+    p.launch_id = g.launch_id;
+    for (int r = 0; r < kMaxReplicas - 1; ++r) p.peer_c[r] = r < g.n_extra_c ? g.extra_c[r] : nullptr;
+    // Forwarding CTAs: with three or more replicas to feed, the bytes leaving for other GPUs are a large share of
+    // the launch and are better sent from SMs of their own (see copy_tiles).  With one or two the epilogue's own
+    // stores cost less than the SMs would.
+    p.copy_ctas = 0;
+    p.tile_flags = nullptr;
+    {
+        const Options& o = options();
+        const bool vec_rows = ((d.n * elem_size(d.c_type)) % 16) == 0;     // the forwarding stores are 16 bytes wide
+        int want = o.gemm_copy_ctas >= 0 ? o.gemm_copy_ctas : (g.n_extra_c >= 6 ? 24 : g.n_extra_c >= 3 ? 18 : 0);
+        want -= want % 2;
+        if (g.n_extra_c > 0 && want > 0 && vec_rows && g.tile_flags && tiles_total <= g.tile_flags_capacity && want + 2 <= g.num_sms) {
+            p.copy_ctas = want;
+            p.tile_flags = g.tile_flags;
+            cudaError_t fe = cudaMemsetAsync(p.tile_flags, 0, (size_t)tiles_total * sizeof(int), g.stream);
+            if (fe != cudaSuccess) { *err = cudaGetErrorString(fe); return ACCB_ERR_CUDA; }
         }
     }
     if (p.pace_pct > 0) {

@@ -373,6 +373,7 @@ extern "C" int accb_reduce_mean_rank3_noalloc(const float* data, int64_t d0, int
                                               int32_t axes_mask, void* cuda_stream)
 {
     using accb::set_error;
+    accb::clear_error();
     if (d0 < 0 || d1 < 0 || d2 < 0) return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: negative dimension");
     if (axes_mask < 0 || axes_mask > 7) return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: axes_mask must be in [0, 7]");
     if (axes_mask == 0) axes_mask = 7;
@@ -383,9 +384,12 @@ extern "C" int accb_reduce_mean_rank3_noalloc(const float* data, int64_t d0, int
     if (d0 * d1 * d2 == 0) return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: mean over zero elements");
     if (!data || !reduced) return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: null array pointer");
 
+    // the device this thread selected with accb_set_device (made current), else the current one: the same
+    // choice every other entry point makes
     int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) { (void)cudaGetLastError(); return set_error(ACCB_ERR_CUDA, cudaGetErrorString(e)); }
+    int rc = accb::selected_device(&dev);
+    if (rc != ACCB_OK) return rc;
+    cudaError_t e = cudaSuccess;
     if (dev < 0 || dev >= kMaxDevicesNoAlloc) return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: device index out of range");
     if (!on_device(data) || !on_device(reduced))
         return set_error(ACCB_ERR_ARG, "accb_reduce_mean_rank3_noalloc: data and reduced must be device memory "
@@ -402,6 +406,10 @@ extern "C" int accb_reduce_mean_rank3_noalloc(const float* data, int64_t d0, int
                 (void)cudaGetLastError();
                 return set_error(ACCB_ERR_CUDA, (std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e)).c_str());
             }
+            int major = 0;
+            e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+            if (e != cudaSuccess) { (void)cudaGetLastError(); return set_error(ACCB_ERR_CUDA, "cudaDeviceGetAttribute(computeCapabilityMajor) failed"); }
+            if (major != 10) return set_error(ACCB_ERR_CUDA, "accb_reduce_mean_rank3_noalloc: this library contains sm_100a code only");
             int n = 0;
             e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
             if (e != cudaSuccess || n <= 0) { (void)cudaGetLastError(); return set_error(ACCB_ERR_CUDA, "cudaDeviceGetAttribute(multiProcessorCount) failed"); }

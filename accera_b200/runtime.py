@@ -31,9 +31,9 @@ _COMPUTE = {"auto": COMPUTE_AUTO, "simt": COMPUTE_SIMT, "tensor": COMPUTE_TENSOR
             "tensor_preferred": COMPUTE_TENSOR_PREFERRED}
 
 EXPORTED_SYMBOLS = (
-    "accb_gemm", "accb_gemm_batched", "accb_gemm_tile_plan", "accb_gemm_replicated", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_noalloc", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
-    "accb_gather_rank2_dims", "accb_range_count_f32", "accb_range_f32", "accb_range_plan_f32", "accb_set_device", "accb_set_stream", "accb_synchronize", "accb_last_error",
-    "accb_launch_count", "accb_release_workspace", "accb_device_count", "accb_version",
+    "accb_gemm", "accb_gemm_batched", "accb_gemm_tile_plan", "accb_gemm_launch_geometry", "accb_gemm_replicated", "accb_reduce_mean_rank3", "accb_reduce_mean_rank3_noalloc", "accb_reduce_mean_rank3_dims", "accb_gather_rank2",
+    "accb_gather_rank2_dims", "accb_range_count_f32", "accb_range_f32", "accb_range_plan_f32", "accb_set_device", "accb_get_device", "accb_current_device", "accb_set_stream", "accb_synchronize", "accb_last_error",
+    "accb_launch_count", "accb_release_workspace", "accb_device_count", "accb_version", "accb_set_option", "accb_debug_decode_status",
 )
 
 
@@ -78,6 +78,9 @@ def lib() -> ctypes.CDLL:
     L.accb_gemm_tile_plan.argtypes = [ctypes.POINTER(GemmDesc), i64, i32, ctypes.POINTER(i32), ctypes.POINTER(i32),
                                       ctypes.POINTER(i64), ctypes.POINTER(i64)]
     L.accb_gemm_tile_plan.restype = ctypes.c_int
+    L.accb_gemm_launch_geometry.argtypes = [ctypes.POINTER(GemmDesc), i64, i32, ctypes.POINTER(i32), ctypes.POINTER(i32),
+                                            ctypes.POINTER(i32)]
+    L.accb_gemm_launch_geometry.restype = ctypes.c_int
     L.accb_gemm_replicated.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp), i32, vp]
     L.accb_gemm_replicated.restype = ctypes.c_int
     L.accb_reduce_mean_rank3.argtypes = [vp, i64, i64, i64, vp, i32]
@@ -98,6 +101,12 @@ def lib() -> ctypes.CDLL:
     L.accb_range_f32.restype = ctypes.c_int
     L.accb_set_device.argtypes = [i32]
     L.accb_set_device.restype = ctypes.c_int
+    L.accb_get_device.restype = ctypes.c_int
+    L.accb_current_device.restype = ctypes.c_int
+    L.accb_set_option.argtypes = [ctypes.c_char_p, i64]
+    L.accb_set_option.restype = ctypes.c_int
+    L.accb_debug_decode_status.argtypes = [ctypes.POINTER(i32), i32, i32, ctypes.c_char_p, i32]
+    L.accb_debug_decode_status.restype = ctypes.c_int
     L.accb_set_stream.argtypes = [vp]
     L.accb_set_stream.restype = ctypes.c_int
     L.accb_synchronize.restype = ctypes.c_int
@@ -127,8 +136,51 @@ def set_device(device: int) -> None:
     _check(lib().accb_set_device(int(device)))
 
 
+def selected_device() -> int:
+    """The device this thread selected with set_device, -1 if none (calls then follow the current CUDA device)."""
+    return int(lib().accb_get_device())
+
+
+def current_device() -> int:
+    """The CUDA runtime's current device of this thread."""
+    d = int(lib().accb_current_device())
+    if d < 0:
+        raise AccbError(d, "no usable CUDA device")
+    return d
+
+
 def set_stream(stream_handle: int) -> None:
     _check(lib().accb_set_stream(ctypes.c_void_p(int(stream_handle) or None)))
+
+
+def set_option(name: str, value: int) -> None:
+    """Per-thread override of a choice the launch code otherwise makes itself (see accb_set_option in
+    include/accera_b200.h); set_option("reset", 0) restores every default."""
+    _check(lib().accb_set_option(name.encode(), int(value)))
+
+
+class options:
+    """Context manager: `with options(**{"gemm.tile_cols": 128}): ...` sets the overrides and resets ALL of them on exit."""
+
+    def __init__(self, **kv):
+        self._kv = kv
+
+    def __enter__(self):
+        for k, v in self._kv.items():
+            set_option(k.replace("__", "."), v)
+        return self
+
+    def __exit__(self, *exc):
+        set_option("reset", 0)
+        return False
+
+
+def decode_status(words, what: int = 0, launch_id: int = 0):
+    """-> (code, message) the library derives from eight device status words (host only; for tests)."""
+    arr = (ctypes.c_int32 * 8)(*[int(w) for w in words])
+    buf = ctypes.create_string_buffer(512)
+    rc = lib().accb_debug_decode_status(arr, int(what), int(launch_id), buf, 512)
+    return int(rc), buf.value.decode()
 
 
 def synchronize() -> None:
@@ -192,13 +244,26 @@ def _raw(x):
 
 
 def _sync_torch_stream(*arrays) -> None:
-    """Device-pointer calls run on torch's current stream of the tensors' device."""
+    """Device-pointer calls run on torch's current stream of the tensors' device; calls on host arrays run on
+    the default stream (a stream selected for an earlier device-pointer call is not carried over: it may
+    belong to another device or no longer exist)."""
     for x in arrays:
         if _is_torch(x) and x.is_cuda:
             import torch
             set_device(x.device.index)
             set_stream(torch.cuda.current_stream(x.device).cuda_stream)
             return
+    set_stream(0)
+
+
+def _captured_selection(*arrays):
+    """-> (device index or None, stream as c_void_p) for a callable that repeats a call on these arrays later:
+    torch's current stream of the tensors' device now; the default stream and no device change for host arrays."""
+    for x in arrays:
+        if _is_torch(x) and x.is_cuda:
+            import torch
+            return x.device.index, ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream or None)
+    return None, ctypes.c_void_p(None)
 
 
 # ---------------------------------------------------------------------------
@@ -268,6 +333,26 @@ def gemm_tile_plan(m: int, n: int, k: int, *, in_type: str = "bfloat16", compute
     return {"cta_pairs": bool(pairs.value), "tile_cols": cols.value, "tiles": tiles.value, "rounds": rounds.value}
 
 
+def gemm_launch_geometry(m: int, n: int, k: int, *, in_type: str = "bfloat16", compute: str = "auto", batch: int = 1,
+                         num_sms: int = 148, b_row_major: bool = False, max_ctas: int = 0) -> dict:
+    """Grid, block and dynamic shared memory of the tensor-core launch for an M x N x K problem (host only):
+    {"grid": [x, y, z], "block": [x, y, z], "dynamic_shared_mem_bytes"}."""
+    d = GemmDesc()
+    d.m, d.n, d.k = m, n, k
+    t = {"bfloat16": BF16, "float16": F16, "float32": F32, "int8": S8, "uint8": U8}[in_type]
+    d.a_type = d.b_type = t
+    d.c_type = S32 if t in (S8, U8) else t
+    d.compute = _COMPUTE[compute]
+    d.a_stride[0], d.a_stride[1] = k, 1
+    d.b_stride[0], d.b_stride[1] = (n, 1) if b_row_major else (1, k)
+    d.c_stride[0], d.c_stride[1] = n, 1
+    d.alpha, d.beta, d.epilogue, d.max_ctas = 1.0, 0.0, EPI_NONE, int(max_ctas)
+    grid, block = (ctypes.c_int32 * 3)(), (ctypes.c_int32 * 3)()
+    smem = ctypes.c_int32()
+    _check(lib().accb_gemm_launch_geometry(ctypes.byref(d), int(batch), int(num_sms), grid, block, ctypes.byref(smem)))
+    return {"grid": list(grid), "block": list(block), "dynamic_shared_mem_bytes": smem.value}
+
+
 def gemm_call(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu: bool = False, compute: str = "auto",
               kind: Optional[str] = None, out_kind: Optional[str] = None, max_ctas: int = 0):
     """-> a zero-argument callable that repeats this GEMM on the same arrays.
@@ -275,15 +360,21 @@ def gemm_call(A, B, C, *, bias=None, alpha: float = 1.0, beta: float = 1.0, relu
     The descriptor is filled and the device / stream selected once, now; each later call is only the C-ABI call,
     which is what a compiled HAT stub does (its descriptor is a constant).  For timing loops and for callers
     that issue the same GEMM many times.  The arrays must stay alive and in place; for device tensors the stream
-    is torch's current stream at the time of THIS call.
+    is torch's current stream at the time of THIS call (it is re-selected before every repeat).
     """
     d, pa, pb, pc, pbias = _gemm_args(A, B, C, bias, alpha, beta, relu, compute, kind, out_kind, max_ctas)
-    _sync_torch_stream(A, B, C)
-    fn = lib().accb_gemm
+    dev, stream = _captured_selection(A, B, C)
+    L = lib()
+    fn = L.accb_gemm
+    set_dev, set_str = L.accb_set_device, L.accb_set_stream
     ref = ctypes.byref(d)
     keep = (A, B, C, bias, d)
 
     def call() -> None:
+        # another call of this thread may have selected a different device or stream in between
+        if dev is not None:
+            set_dev(dev)
+        set_str(stream)
         rc = fn(ref, pa, pb, pc, pbias)
         if rc < 0:
             _check(rc)

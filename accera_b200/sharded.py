@@ -31,12 +31,68 @@ Two ways to move the blocks, chosen with `gather=`:
                  staging go to the local C and, over NVLink, to each peer's C, so the transfer overlaps
                  the math tile by tile.  One barrier at the end of the step.
 
+                 With three or more peers the kernel sets a few CTAs aside that do nothing but forward
+                 finished tiles (stores that wait for NVLink would otherwise hold up the operand fetches
+                 of the SM that issued them); with one or two peers the epilogue stores to them directly.
+
 The kernels never load from another GPU's memory and use no TMA multicast; "fused" only stores to it.
+
+Ordering between steps.  "copy_engine" and "fused" write straight into the peers' C.  A rank must not start
+writing step n+1 into a peer's C while that peer still reads step n's result, so both modes open a step
+with a barrier (every rank's consumers of the previous C were enqueued before it reaches that barrier) and
+close it with one (all tiles of this step have landed everywhere).  "nccl" needs neither: the collective
+itself waits for every rank.
+
+Failures are detected on the host: `rendezvous` bounds the time a rank waits for the others to join, and
+`ShardedGemm.run` compares the shard geometry of all ranks before its first collective.
 """
 from __future__ import annotations
 
 import dataclasses
+import datetime
 from typing import Callable, List, Optional, Tuple
+
+
+class ShardMismatchError(RuntimeError):
+    """The ranks of a sharded GEMM do not agree on the problem (raised on every rank, before any collective)."""
+
+
+class RankJoinTimeout(RuntimeError):
+    """A rank did not join the process group, or a barrier, within the time allowed."""
+
+
+def rendezvous(backend: str, rank: int, world: int, timeout_s: float = 600.0, init_method: Optional[str] = None,
+               device_id=None):
+    """torch.distributed.init_process_group with a bound on how long this rank waits for the others.
+
+    A rank that never starts (crashed before joining, wrong world size) makes every other rank raise
+    RankJoinTimeout after `timeout_s` instead of waiting forever.  MASTER_ADDR / MASTER_PORT come from the
+    environment unless `init_method` is given.
+    """
+    import torch.distributed as dist
+    kwargs = dict(backend=backend, rank=rank, world_size=world, timeout=datetime.timedelta(seconds=float(timeout_s)))
+    if init_method is not None:
+        kwargs["init_method"] = init_method
+    if device_id is not None:
+        kwargs["device_id"] = device_id
+    try:
+        dist.init_process_group(**kwargs)
+    except Exception as exc:      # torch raises DistStoreError / DistNetworkError / RuntimeError depending on where it gave up
+        raise RankJoinTimeout(f"rank {rank} of {world}: the process group did not form within {timeout_s:g} s ({exc})") from exc
+    return dist.group.WORLD
+
+
+def checked_barrier(group=None, timeout_s: float = 60.0) -> None:
+    """A host-side barrier that names the ranks that did not arrive within `timeout_s` (gloo groups;
+    other backends fall back to their own barrier and the group's timeout)."""
+    import torch.distributed as dist
+    try:
+        if dist.get_backend(group) == "gloo":
+            dist.monitored_barrier(group=group, timeout=datetime.timedelta(seconds=float(timeout_s)), wait_all_ranks=True)
+        else:
+            dist.barrier(group=group)
+    except Exception as exc:
+        raise RankJoinTimeout(f"barrier: not every rank arrived within {timeout_s:g} s ({exc})") from exc
 
 
 @dataclasses.dataclass(frozen=True)
@@ -131,6 +187,40 @@ class ShardedGemm:
         self._symm = None          # symmetric-memory handle of C (copy_engine)
         self._peer_c: List = []
         self._peer_streams: List = []
+        self._validated = None     # signature of the operands the ranks last agreed on
+
+    def validate(self, a_local, b, c_full) -> None:
+        """Compares the shard geometry of all ranks on the host (one all_gather_object) and raises
+        ShardMismatchError on EVERY rank when they differ: a rank with a shard of another size, another K, N
+        or element type would otherwise make the all-gather write past its blocks, or hang it."""
+        sig = (tuple(a_local.shape), tuple(b.shape), tuple(c_full.shape), str(a_local.dtype), str(c_full.dtype),
+               self.plan.m, self.plan.world, self.plan.chunks)
+        if sig == self._validated:
+            return
+        plan = self.plan
+        problems = []
+        if tuple(a_local.shape)[0] != plan.rows_per_rank:
+            problems.append(f"A shard has {tuple(a_local.shape)[0]} rows, the plan gives every rank {plan.rows_per_rank}")
+        if tuple(c_full.shape)[0] != plan.m:
+            problems.append(f"C has {tuple(c_full.shape)[0]} rows, the plan says {plan.m}")
+        if len(a_local.shape) != 2 or len(b.shape) != 2 or a_local.shape[1] != b.shape[0] or b.shape[1] != c_full.shape[1]:
+            problems.append(f"inner dimensions disagree: A{tuple(a_local.shape)} B{tuple(b.shape)} C{tuple(c_full.shape)}")
+        mine = {"rank": self.rank, "sig": sig, "problems": problems}
+        if plan.world > 1:
+            import torch.distributed as dist
+            everyone = [None] * plan.world
+            dist.all_gather_object(everyone, mine, group=self.group)
+        else:
+            everyone = [mine]
+        bad = [e for e in everyone if e["problems"]]
+        differing = [e["rank"] for e in everyone if e["sig"] != everyone[0]["sig"]]
+        if bad or differing:
+            lines = [f"rank {e['rank']}: {'; '.join(e['problems'])}" for e in bad]
+            if differing:
+                lines.append(f"ranks {differing} describe another problem than rank {everyone[0]['rank']}: "
+                             + ", ".join(f"rank {e['rank']} {e['sig'][:5]}" for e in everyone))
+            raise ShardMismatchError("sharded GEMM: the ranks do not agree - " + " | ".join(lines))
+        self._validated = sig
 
     @staticmethod
     def allocate_c(m: int, n: int, dtype, device, group=None, gather: str = "nccl"):
@@ -165,6 +255,7 @@ class ShardedGemm:
         import torch
         import torch.distributed as dist
         plan = self.plan
+        self.validate(a_local, b, c_full)
         gemm = self._gemm_fn or self._default_gemm
         on_gpu = bool(getattr(c_full, "is_cuda", False))
         if self.gather == "copy_engine" and plan.world > 1:
@@ -205,6 +296,8 @@ class ShardedGemm:
         if self._symm is None:
             self._setup_copy_engine(c_full)
         main = torch.cuda.current_stream(c_full.device)
+        # no peer may still be reading the previous step's C when my pushes start to overwrite it
+        self._symm.barrier()
         for j in range(plan.chunks):
             l0, l1 = plan.local_row_range(j)
             g0, g1 = plan.global_row_range(self.rank, j)
@@ -229,6 +322,8 @@ class ShardedGemm:
         if self._symm is None:
             self._setup_copy_engine(c_full)
         kw = {k: v for k, v in self.gemm_kwargs.items() if k in ("alpha", "beta", "relu", "compute", "max_ctas", "bias")}
+        # no peer may still be reading the previous step's C when my kernel starts to overwrite its blocks there
+        self._symm.barrier()
         for j in range(plan.chunks):
             l0, l1 = plan.local_row_range(j)
             g0, g1 = plan.global_row_range(self.rank, j)

@@ -124,6 +124,16 @@ int accb_gemm_tile_plan(const accb_gemm_desc* desc, int64_t batch, int32_t num_s
                         int64_t* tiles, int64_t* rounds);
 
 /*
+ * Host-only helper (no GPU needed): the launch the tensor-core path makes for `desc` x `batch` on a device with
+ * `num_sms` SMs - grid[3], block[3] and the dynamic shared memory of the kernel.  This is the information the
+ * reference records per GPU function as launch_parameters / dynamic_shared_mem_bytes
+ * (accera/python/accera/Package.py:714-743, derived there from accera/python/accera/lang/Plan.py:879-956); here the
+ * kernel is persistent, so the grid follows from the SM count and the tile plan, not from the problem alone.
+ */
+int accb_gemm_launch_geometry(const accb_gemm_desc* desc, int64_t batch, int32_t num_sms, int32_t* grid, int32_t* block,
+                              int32_t* dynamic_shared_mem_bytes);
+
+/*
  * The same GEMM on the tensor cores, with the result stored to several replicas of C at once.
  * (No counterpart in the reference, which has no multi-GPU path.)  c_replicas[0] is the local C: it is
  * read when beta != 0 and written; c_replicas[1..n_replicas-1] receive the same values with the same
@@ -227,7 +237,10 @@ int64_t accb_range_plan_f32(float start, float delta, int64_t n, int64_t* first,
  * (device selection and synchronisation, tools/benchmarkers/accera_gemm.py:612-626)
  * and accera/runtime; none of them appears in a HAT prototype.
  */
-int accb_set_device(int32_t device);      /* device used by this thread's following calls */
+int accb_set_device(int32_t device);      /* device used by this thread's following calls (made current); -1 = no
+                                             selection, follow the current CUDA device again */
+int accb_get_device(void);                /* this thread's selection, -1 if none */
+int accb_current_device(void);            /* the CUDA runtime's current device of this thread, or ACCB_ERR_CUDA */
 int accb_set_stream(void* cuda_stream);   /* cudaStream_t used for device-pointer calls; NULL = default stream */
 int accb_synchronize(void);               /* wait for the selected stream; reports deferred device-side errors */
 const char* accb_last_error(void);        /* text of the last error on this thread ("" if none) */
@@ -235,6 +248,39 @@ int64_t accb_launch_count(void);          /* kernels launched by this library so
 int accb_release_workspace(void);         /* free the cached staging buffers of the current device */
 int accb_device_count(void);              /* number of visible CUDA devices, 0 if none / no driver */
 const char* accb_version(void);
+
+/*
+ * Errors that happen ON the device - a bounded wait of the tensor-core GEMM that ran out (ACCB_ERR_TIMEOUT), a
+ * gather index outside the data (ACCB_ERR_INDEX) - are written by the kernel into a per-device status record
+ * together with the id of the launch that had them.  A call on HOST pointers is synchronous and returns its own
+ * launches' errors.  A call on DEVICE pointers only enqueues work: its device-side errors are DEFERRED and are
+ * returned (and cleared) by the next accb_synchronize() on that device; they are never attributed to a later call,
+ * and a failure that has not been collected yet does not disturb later launches.
+ *
+ * Per-thread overrides of choices the launch code otherwise makes by itself.  They exist so that tests reach every
+ * code path on small problems, for tuning runs, and for the self-test of the time-out path; none is needed in
+ * normal use and none has a counterpart in the reference.  accb_set_option("reset", 0) restores all defaults.
+ *   "gemm.tile_cols"         0 (choose) | 128 | 256   accumulator columns per tile of the tensor-core GEMM
+ *   "gemm.staged_store"      -1 (choose) | 0 | 1      epilogue through shared memory + TMA stores (1) or from registers (0)
+ *   "gemm.pace_pct"          -1 (choose) | 0..100     tile-by-tile pacing of the persistent CTAs
+ *   "gemm.group_m"           0 (choose) | rows        tile rows visited together
+ *   "gemm.hint_a" / "gemm.hint_b"   0 | 1 | 2         L2 eviction priority of the operand loads
+ *   "gemm.c_stream"          0 | 1                    streaming accesses to C
+ *   "gemm.peer_store"        -1 (choose) | 0 | 1      accb_gemm_replicated: TMA stores (0) or register stores (1) to peers
+ *   "gemm.copy_ctas"         -1 (choose) | 0..128     accb_gemm_replicated: CTAs set aside to forward finished tiles to the
+ *                                                     replicas (0: the computing CTAs store to every replica themselves)
+ *   "gemm.wait_limit_us"     0 (one second) | us      limit of every bounded device-side wait
+ *   "gemm.test_drop_commit"  0 | 1                    self-test: each CTA's last accumulator is never signalled complete,
+ *                                                     so the epilogue's bounded wait runs out and the launch reports
+ *                                                     ACCB_ERR_TIMEOUT (no fault, no trap; the context stays usable)
+ *   "gemm.verbose"           0 | 1                    print the launch plan to stderr
+ *   "host_gemm.stage_chunks" 0 (16) | 1..256          row chunks of the staged host-pointer GEMM
+ */
+int accb_set_option(const char* name, int64_t value);
+
+/* Test hook: decodes eight status words as the library would (what: 0 everything, 1 the GEMM launch `launch_id`,
+ * 2 the gather launch `launch_id`); returns the ACCB_* code and writes the message.  Host only. */
+int accb_debug_decode_status(const int32_t* words, int32_t what, int32_t launch_id, char* message, int32_t capacity);
 
 #if defined(__cplusplus)
 } /* extern "C" */

@@ -556,25 +556,24 @@ def test_gemm_replicated_writes_every_replica(kind, out_kind, m, n, k):
         assert np.abs(gf - wf).max() <= 2e-2 * max(1.0, np.abs(wf).max())
 
 
-def test_direct_store_epilogue_still_matches(monkeypatch):
+def test_direct_store_epilogue_still_matches():
     # the epilogue without shared-memory staging (column-major or unaligned C), forced on an aligned C
-    monkeypatch.setenv("ACCB_GEMM_TUNE", "t=0")
-    _tensor_case("bfloat16", "bfloat16", 384, 520, 320, "tensor_2sm", beta=1.0, use_bias=True)
-    _tensor_case("float16", "float32", 200, 300, 136, "tensor", beta=1.0)
-    _tensor_case("bfloat16", "bfloat16", 4096, 2304, 192, "tensor_2sm", beta=1.0)
-    monkeypatch.delenv("ACCB_GEMM_TUNE")
+    with rt.options(**{"gemm.staged_store": 0}):
+        _tensor_case("bfloat16", "bfloat16", 384, 520, 320, "tensor_2sm", beta=1.0, use_bias=True)
+        _tensor_case("float16", "float32", 200, 300, 136, "tensor", beta=1.0)
+        _tensor_case("bfloat16", "bfloat16", 4096, 2304, 192, "tensor_2sm", beta=1.0)
     _tensor_case("bfloat16", "bfloat16", 384, 520, 320, "tensor_2sm", beta=1.0, use_bias=True)
 
 
-@pytest.mark.parametrize("store", ["t=1", "t=0"])
+@pytest.mark.parametrize("store", [1, 0])
 @pytest.mark.parametrize("compute", TENSOR_MODES)
 @pytest.mark.parametrize("kind,out_kind", [("bfloat16", "bfloat16"), ("float16", "float32"), ("float16", "float16"),
                                            ("int8", "int32"), ("float32", "float32")])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (384, 520, 320), (200, 300, 144), (1, 8, 16), (129, 257, 80)])
-def test_both_epilogue_paths_on_ragged_shapes(monkeypatch, store, compute, kind, out_kind, m, n, k):
-    # staged TMA stores (t=1, the default for a storable C) and stores straight from registers (t=0) on the same shapes
-    monkeypatch.setenv("ACCB_GEMM_TUNE", store)
-    _tensor_case(kind, out_kind, m, n, k, compute, beta=1.0, relu=True, use_bias=(kind != "int8"), alpha=1.0 if kind == "int8" else 0.5)
+def test_both_epilogue_paths_on_ragged_shapes(store, compute, kind, out_kind, m, n, k):
+    # staged TMA stores (1, the default for a storable C) and stores straight from registers (0) on the same shapes
+    with rt.options(**{"gemm.staged_store": store}):
+        _tensor_case(kind, out_kind, m, n, k, compute, beta=1.0, relu=True, use_bias=(kind != "int8"), alpha=1.0 if kind == "int8" else 0.5)
 
 
 def test_tensor_gemm_random_shapes_fuzz():
@@ -662,7 +661,7 @@ def test_tensor_awkward_tile_counts(compute, kind, out_kind, m, n, k):
     _tensor_case(kind, out_kind, m, n, k, compute, beta=1.0, relu=True, use_bias=(kind != "int8"), alpha=1.0 if kind == "int8" else 0.5)
 
 
-def test_tile_width_does_not_change_the_result(monkeypatch):
+def test_tile_width_does_not_change_the_result():
     # 128- and 256-column tiles accumulate every output element over K in the same order: identical bits
     import torch
     dev = torch.device("cuda:0")
@@ -675,11 +674,11 @@ def test_tile_width_does_not_change_the_result(monkeypatch):
     for a, b, cdt in ((A8, B8, torch.int32), (A, B, torch.float32), (A, B, torch.bfloat16)):
         for compute in TENSOR_MODES:
             outs = []
-            for tune in ("n=256", "n=128"):
-                monkeypatch.setenv("ACCB_GEMM_TUNE", tune)
-                C = torch.zeros(m, n, device=dev, dtype=cdt)
-                rt.gemm(a, b, C, beta=0.0, compute=compute)
-                rt.synchronize()
+            for cols in (256, 128):
+                with rt.options(**{"gemm.tile_cols": cols}):
+                    C = torch.zeros(m, n, device=dev, dtype=cdt)
+                    rt.gemm(a, b, C, beta=0.0, compute=compute)
+                    rt.synchronize()
                 outs.append(C.clone())
             assert torch.equal(outs[0], outs[1]), (cdt, compute)
 

@@ -654,8 +654,8 @@ void (*tiled_mm_py)(float*, float*, float*) = tiled_mm_py_0badc0de;
     assert again.functions[0].arguments == f.arguments and again.dependencies == hf.dependencies
 
 
-def test_gemm_tile_plan_is_host_only_and_follows_the_cost_model(monkeypatch):
-    monkeypatch.delenv("ACCB_GEMM_TUNE", raising=False)
+def test_gemm_tile_plan_is_host_only_and_follows_the_cost_model():
+    runtime.set_option("reset", 0)
     plan = runtime.gemm_tile_plan
     # the benchmark problem: 256 x 256 pair tiles, 8192 of them on 74 pairs
     assert plan(65536, 8192, 8192) == {"cta_pairs": True, "tile_cols": 256, "tiles": 8192, "rounds": 111}

@@ -65,13 +65,8 @@ def _worker(rank, world, port, chunks, tmpdir):
         c_full = torch.full((m, n), float("nan"))
         ShardedGemm(plan, rank, gemm_fn=gemm_fn).run(a_local, torch.from_numpy(np.ascontiguousarray(b)), c_full)
         ok = np.array_equal(c_full.numpy(), want)
-        # a mismatch of shard shapes among ranks must be caught on the host, before any collective
-        flag = torch.tensor([plan.rows_per_rank + (1 if (rank == 1 and chunks == 99) else 0)])
-        gathered = [torch.zeros_like(flag) for _ in range(world)]
-        dist.all_gather(gathered, flag)
-        same = all(int(g) == int(flag) for g in gathered)
         with open(os.path.join(tmpdir, f"r{rank}.txt"), "w") as f:
-            f.write("ok" if (ok and same) else f"bad ok={ok} same={same}")
+            f.write("ok" if ok else "bad")
     finally:
         dist.destroy_process_group()
 
@@ -82,3 +77,94 @@ def test_sharded_gemm_gloo(tmp_path, world, chunks):
     mp.spawn(_worker, args=(world, port, chunks, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert (tmp_path / f"r{r}.txt").read_text() == "ok"
+
+
+def _mismatch_worker(rank, world, port, tmpdir, what):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    from accera_b200.sharded import ShardMismatchError, rendezvous
+    rendezvous("gloo", rank, world, timeout_s=60)
+    try:
+        m, n, k = 64, 24, 40
+        plan = RowBlockPlan(m, world, 2)
+        rows = plan.rows_per_rank
+        kk = k
+        if what == "rows" and rank == 1:
+            rows += 16                      # rank 1 brings a shard of another size
+        if what == "k" and rank == 1:
+            kk = k + 8                      # rank 1 was built for another K
+        a_local = torch.zeros(rows, kk)
+        b = torch.zeros(kk, n)
+        c_full = torch.zeros(m, n)
+        calls = []
+        sg = ShardedGemm(plan, rank, gemm_fn=lambda a, bb, c: calls.append(1))
+        try:
+            sg.run(a_local, b, c_full)
+            outcome = "no error"
+        except ShardMismatchError as exc:
+            outcome = f"caught calls={len(calls)} names_rank1={'rank 1' in str(exc)}"
+        with open(os.path.join(tmpdir, f"r{rank}.txt"), "w") as f:
+            f.write(outcome)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("what", ["rows", "k"])
+def test_shard_mismatch_is_caught_on_every_rank_before_any_work(tmp_path, what):
+    # one rank disagrees about the problem: every rank (also the ones whose own shard is fine) raises before a
+    # GEMM is launched or a collective on C is entered
+    world = 2
+    mp.spawn(_mismatch_worker, args=(world, 29650 + (what == "k"), str(tmp_path), what), nprocs=world, join=True)
+    for r in range(world):
+        assert (tmp_path / f"r{r}.txt").read_text() == "caught calls=0 names_rank1=True"
+
+
+def _late_worker(rank, world, port, tmpdir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import time
+    from accera_b200.sharded import RankJoinTimeout, rendezvous
+    if rank == world - 1:
+        return                              # this rank dies before it joins
+    t0 = time.time()
+    try:
+        rendezvous("gloo", rank, world, timeout_s=4)
+        outcome = "joined"
+    except RankJoinTimeout:
+        outcome = "timeout"
+    with open(os.path.join(tmpdir, f"r{rank}.txt"), "w") as f:
+        f.write(f"{outcome} {time.time() - t0 < 60}")
+
+
+def test_a_rank_that_never_joins_ends_the_others_with_a_timeout(tmp_path):
+    world = 3
+    mp.spawn(_late_worker, args=(world, 29670, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world - 1):
+        assert (tmp_path / f"r{r}.txt").read_text() == "timeout True"
+
+
+def _barrier_worker(rank, world, port, tmpdir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import time
+    from accera_b200.sharded import RankJoinTimeout, checked_barrier, rendezvous
+    rendezvous("gloo", rank, world, timeout_s=60)
+    checked_barrier(timeout_s=30)           # everyone is here: passes
+    outcome = "passed"
+    if rank == 1:
+        time.sleep(6)                       # rank 1 leaves between steps (nothing of it in flight) ...
+    else:
+        try:
+            checked_barrier(timeout_s=2)    # ... and the others learn of it on the host
+        except RankJoinTimeout as exc:
+            outcome = "timeout"
+    with open(os.path.join(tmpdir, f"r{rank}.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)                             # the group is broken: leave without the collective shutdown
+
+
+def test_checked_barrier_reports_a_rank_that_left(tmp_path):
+    world = 2
+    mp.spawn(_barrier_worker, args=(world, 29680, str(tmp_path)), nprocs=world, join=True)
+    assert (tmp_path / "r0.txt").read_text() == "timeout"
+    assert (tmp_path / "r1.txt").read_text() == "passed"
