@@ -165,11 +165,12 @@ int decode_status(const int* w, int what, int id, bool* clear_gemm, bool* clear_
     const bool gemm_mine = what == COLLECT_ALL || (what == COLLECT_GEMM && w[ST_GEMM_ID] == id);
     if (gemm_failed && gemm_mine) {
         static const char* sites[] = { "?", "producer waiting for a free stage", "MMA waiting for operands",
-                                       "MMA waiting for a free accumulator", "epilogue waiting for the accumulator" };
+                                       "MMA waiting for a free accumulator", "epilogue waiting for the accumulator",
+                                       "forwarding CTA waiting for a tile" };
         const int site = (w[ST_GEMM_SITE] >> 24) & 0xff;
         char buf[256];
         snprintf(buf, sizeof buf, "tcgen05 GEMM (launch %d): bounded wait ran out (%s, block %d, step %d; %d wait(s) in all); "
-                 "results are invalid", w[ST_GEMM_ID], site >= 1 && site <= 4 ? sites[site] : sites[0],
+                 "results are invalid", w[ST_GEMM_ID], site >= 1 && site <= 5 ? sites[site] : sites[0],
                  w[ST_GEMM_SITE] & 0xffffff, w[ST_GEMM_STEP], w[ST_GEMM_COUNT]);
         *msg = buf;
         *clear_gemm = true;

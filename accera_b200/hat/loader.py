@@ -139,22 +139,39 @@ class HATFunction:
         if tensors:
             # device buffers: the kernels go to torch's current stream of that device
             runtime._sync_torch_stream(*tensors)
-        elif device_id is not None:
-            # host arrays: staged through, and computed on, the GPU the caller names (hatlib's device_id argument,
-            # tools/benchmarkers/accera_gemm.py:614)
-            runtime.set_device(int(device_id))
-        self._symbol(*c_args)
+            self._symbol(*c_args)
+            return
+        runtime.set_stream(0)                 # host arrays run on the default stream, whatever was selected before
+        if device_id is None:
+            self._symbol(*c_args)
+            return
+        # host arrays: staged through, and computed on, the GPU the caller names (hatlib's device_id argument,
+        # tools/benchmarkers/accera_gemm.py:614) - for this call only: the thread's selection and the CUDA
+        # runtime's current device are put back afterwards
+        selected, current = runtime.selected_device(), runtime.current_device()
+        runtime.set_device(int(device_id))
+        try:
+            self._symbol(*c_args)
+        finally:
+            runtime.set_device(current)
+            if selected < 0:
+                runtime.set_device(-1)
 
     def bind(self, *args):
         """-> zero-argument callable repeating this call on the same arguments (marshalled and checked once)."""
         c_args, keep = self._marshal(args)
         tensors = [a for a in keep if _is_torch(a)]
-        if tensors:
-            from .. import runtime
-            runtime._sync_torch_stream(*tensors)
+        from .. import runtime
+        dev, stream = runtime._captured_selection(*tensors)
+        L = runtime.lib()
+        set_dev, set_str = L.accb_set_device, L.accb_set_stream
         symbol = self._symbol
 
         def call() -> None:
+            # the device and stream of the arguments, re-selected: another call may have changed them in between
+            if dev is not None:
+                set_dev(dev)
+            set_str(stream)
             symbol(*c_args)
         call.keep_alive = (keep, args)
         return call
@@ -203,13 +220,25 @@ class FunctionMap:
 
 
 class HATPackage:
-    def __init__(self, hat: HATFile, library: ctypes.CDLL):
+    """A `.hat` file and, once loaded, its library.  `HATPackage(path)` only reads the descriptor, which is how
+    the reference's tests inspect a built package (dsl_tests.py:5834-5842); `load` returns one with the library."""
+
+    def __init__(self, hat, library: Optional[ctypes.CDLL] = None):
+        if not isinstance(hat, HATFile):
+            hat = HATFile.Deserialize(str(hat))
         self.hat_file = hat
+        self.hat_file_path = hat.path
         self.library = library
         self.name = hat.name
 
     def get_functions(self) -> List[Function]:
         return list(self.hat_file.functions)
+
+    def get_function(self, name: str) -> Optional[Function]:
+        return self.hat_file.function_map.get(name)
+
+    def get_functions_for_base_name(self, base_name: str) -> List[Function]:
+        return [f for f in self.hat_file.functions if f.name == base_name or f.name.rsplit("_", 1)[0] == base_name]
 
 
 def _aliases(hat: HATFile) -> Dict[str, str]:
@@ -266,8 +295,29 @@ class BenchmarkResult:
         return dataclasses.asdict(self)
 
 
+def _index_bound(fn: Function, values: Dict[str, int], dim_value: int) -> int:
+    """Upper bound for generated gather indices: the gathered dimension of the data array (so that a benchmark does
+    not time the out-of-range path)."""
+    op = fn.auxiliary.get("accera_b200", {})
+    if op.get("op") != "gather":
+        return dim_value
+    axis = int(op.get("axis", 0))
+    for p in fn.arguments:
+        if p.logical_type == "element" or p.usage != "input" or p.element_type == "int64_t":
+            continue
+        if p.logical_type == "affine_array" and p.shape and len(p.shape) == 2:
+            return int(p.shape[axis])
+        if p.logical_type == "runtime_array" and p.size:
+            names = [t.strip() for t in p.size.split("*")]
+            if len(names) == 2:
+                tok = names[axis]
+                return int(tok) if re.fullmatch(r"\d+", tok) else int(values.get(tok, dim_value))
+    return dim_value
+
+
 def generate_arg_values(fn: Function, rng: np.random.Generator, dim_value: int = 128):
-    """Random inputs matching a function's descriptor (dimension arguments get `dim_value`)."""
+    """Random inputs matching a function's descriptor (dimension arguments get `dim_value`; gather indices stay
+    inside the gathered dimension)."""
     values: Dict[str, int] = {}
     for p in fn.arguments:
         if p.logical_type == "element" and p.usage == "input":
@@ -292,7 +342,7 @@ def generate_arg_values(fn: Function, rng: np.random.Generator, dim_value: int =
         elif np.issubdtype(dt, np.floating):
             a = rng.random(shape).astype(dt)
         elif p.usage == "input" and "index" in p.name.lower() or (p.usage == "input" and dt == np.int64):
-            a = rng.integers(0, dim_value, size=shape).astype(dt)       # valid gather indices
+            a = rng.integers(0, max(1, _index_bound(fn, values, dim_value)), size=shape).astype(dt)       # valid gather indices
         else:
             info = np.iinfo(dt)
             a = rng.integers(max(info.min, -4), min(info.max, 4), size=shape).astype(dt)
@@ -369,15 +419,15 @@ def run_benchmark(hat_path: str, store_in_hat: bool = False, batch_size: int = 1
     """Times every function of the package: batches of `batch_size` calls until `min_time_in_sec` has
     elapsed (at least 3 batches).  device_resident=True times on GPU-resident buffers with CUDA events, False on
     host arrays (each call then includes the library's host<->device staging).  The default follows hatlib: functions
-    of a GPU-target package (those that name the device kernel they launch) are timed on the device, the others on
-    host arrays."""
+    built for a GPU target are timed on the device, the others on host arrays."""
     _, fmap = load(hat_path)
     rng = np.random.default_rng(0)
     results = []
     for fn in fmap:
         if functions and fn.name not in functions:
             continue
-        on_device = device_resident if device_resident is not None else bool(fn.desc.launches)
+        gpu_function = bool(fn.desc.launches) or fn.desc.auxiliary.get("accera_b200", {}).get("runtime") == "CUDA"
+        on_device = device_resident if device_resident is not None else gpu_function
         if on_device:
             r = BenchmarkResult.from_batch_means(fn.name, _run_benchmark_on_device(fn, rng, batch_size, min_time_in_sec,
                                                                   input_sets_minimum_size_MB, device_id))

@@ -195,6 +195,14 @@ class Target:
         self.runtime = "CUDA" if self.category is Target.Category.GPU else "NONE"
         self.extra = dict(kwargs)
         self.tensor_core_info = _TensorCoreInfo()
+        # launch limits the reference checks a bound plan against (Targets.py: "Max Block Size", "Max Threads Per
+        # Block", "Warp Size"; lang/Plan.py:989-1011).  The CUDA values hold for every NVIDIA model listed here.
+        gpu = self.category is Target.Category.GPU
+        amd = known_name is Target.Model.AMD_MI100
+        self.warp_size = kwargs.get("warp_size", (64 if amd else 32) if gpu else 0)
+        self.max_threads_per_block = kwargs.get("max_threads_per_block", 1024 if gpu else 0)
+        self.max_block_size = list(kwargs.get("max_block_size", [1024, 1024, 64] if gpu else []))
+        self.num_sms = kwargs.get("num_sms", 148 if known_name is Target.Model.NVIDIA_B200 else 0)
 
     def is_compatible_with(self, other: "Target") -> bool:
         return self.category == other.category and self.runtime == other.runtime
@@ -567,7 +575,24 @@ class Schedule:
     def _new_index(self, parent: Index, size) -> Index:
         idx = Index(size, None, -1, parent.name + parent.name[-1])
         self._indices.insert(self._indices.index(parent) + 1, idx)
+        # the parent now advances `size` at a time; the new index walks one block of it
+        steps = self.__dict__.setdefault("_steps", {})
+        steps[id(parent)] = steps.get(id(parent), 1) * int(size)
+        self.__dict__.setdefault("_split_factor", {})[id(idx)] = int(size)
         return idx
+
+    def iteration_count(self, index: Index) -> int:
+        """Iterations of `index` in this schedule: its split factor if it came from a split and was not split
+        again, else ceil(extent / step) (lang/Plan.py:888-893)."""
+        steps = self.__dict__.get("_steps", {})
+        step = steps.get(id(index), 1)
+        factor = self.__dict__.get("_split_factor", {}).get(id(index))
+        if step == 1 and factor is not None:
+            return factor
+        extent = index.extent
+        if not isinstance(extent, int):
+            raise ValueError("launch geometry needs static extents")
+        return -(-extent // step)
 
     def split(self, index: Index, size) -> Index:
         self.transformations.append(("split", (index, size)))
@@ -644,6 +669,7 @@ class Plan:
         self.schedule = schedule
         self.target = target
         self.options: List[Tuple[str, Any]] = []
+        self.bindings: Dict[Any, Any] = {}
         self.tensorized = False
         self.prologue_op = MMAFragmentOp.NONE
         self.prologue_arg = 0.0
@@ -656,7 +682,73 @@ class Plan:
     def kernelize(self, unroll_indices, vectorize_indices=None): self.options.append(("kernelize", unroll_indices))
 
     def bind(self, mapping=None, **kwargs):
+        """Binds schedule indices (or tuples of them) to grid units (lang/Plan.py:793-825).  The hand-written
+        kernels choose their own launch geometry, so the binding does not steer them; it is kept, turned into the
+        block and grid it asks for, and checked against the target's limits when the plan is added to a package,
+        which is where the reference rejects an impossible launch too (lang/Plan.py:989-1004)."""
+        if self.target is None or self.target.category is not Target.Category.GPU:
+            raise ValueError("Only supported on plans with GPU targets")
+        mapping = dict(mapping or {})
+        for index_or_tuple, proc in mapping.items():
+            if not isinstance(proc, Target.GridUnit):
+                raise TypeError("bind maps indices to Target.GridUnit values")
+            self.bindings[proc] = index_or_tuple
         self.options.append(("bind", mapping))
+
+    def launch_request(self):
+        """-> (block_dims, grid_dims) the plan's bindings and splits ask for (lang/Plan.py:879-956): block units
+        give the grid, thread units the block, warp units a block of (warps_x * warp_size, warps_y, 1); without
+        bindings a 16 x 16 block whose sides follow the split factors of the first two nest dimensions."""
+        sched = self.schedule
+        units = Target.GridUnit
+
+        def fill(unit_list, dims):
+            for pos, u in enumerate(unit_list):
+                bound = self.bindings.get(u)
+                if bound is None:
+                    continue
+                if not isinstance(bound, (tuple, list)):
+                    bound = (bound,)
+                n = 1
+                for ix in bound:
+                    n *= sched.iteration_count(ix)
+                dims[pos] = n
+
+        block, grid, warps = [1, 1, 1], [1, 1, 1], [0, 0]
+        if self.bindings:
+            fill([units.BLOCK_X, units.BLOCK_Y, units.BLOCK_Z], grid)
+            fill([units.THREAD_X, units.THREAD_Y, units.THREAD_Z], block)
+            fill([units.WARP_X, units.WARP_Y], warps)
+            if any(warps):
+                block = [warps[0] * self.target.warp_size, warps[1], 1]
+        else:
+            block = [16, 16, 1]
+            nest = sched.nests[0]
+            factors = sched.__dict__.get("_split_factor", {})
+            children = {}
+            for ix in sched.get_indices():
+                if id(ix) in factors:
+                    children.setdefault(ix.name[:-1], factors[id(ix)])
+            for pos, ix in enumerate(nest._indices[:2]):
+                if ix.name in children:
+                    block[pos] = children[ix.name]
+                if isinstance(ix.extent, int):
+                    grid[pos] = -(-ix.extent // block[pos])
+        return block, grid
+
+    def check_launch_request(self) -> None:
+        """Raises ValueError for a block the target cannot run (lang/Plan.py:958-1004, same messages)."""
+        if self.target is None or self.target.category is not Target.Category.GPU:
+            return
+        try:
+            block, _ = self.launch_request()
+        except ValueError:
+            return                              # runtime-sized nests: nothing static to check
+        limit = self.target.max_block_size
+        if len(limit) == 3 and any(block[i] > limit[i] for i in range(3)):
+            raise ValueError(f"Invalid block dimensions: {block}. Largest supported block dimensions: {limit}.")
+        if self.target.max_threads_per_block and block[0] * block[1] * block[2] > self.target.max_threads_per_block:
+            raise ValueError(f"Invalid block size {block}. Max threads per block: {self.target.max_threads_per_block}.")
 
     def cache(self, source, index=None, trigger_index=None, layout=None, max_elements=None, element_type=None,
               thrifty=None, location=_MemorySpace.NONE, level=None, trigger_level=None, double_buffer=False,

@@ -25,7 +25,7 @@ from collections import OrderedDict
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 from . import lang, patterns
-from .hat import hat_file
+from .hat import hat_file, packaging
 from .lang import Array, Dimension, Role, Scalar, ScalarType, Target
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
@@ -44,6 +44,7 @@ class _PackagedFunction:
         self.args = list(args)
         self.target = target
         self.auxiliary = auxiliary
+        self.launch_request = None      # (block, grid) a bound GPU plan asked for
 
 
 class Package:
@@ -91,7 +92,13 @@ class Package:
                 raise ValueError("TEMP scalars cannot be function arguments")
             if not isinstance(a, (Array, Dimension, Scalar)):
                 raise TypeError("args may contain Arrays, Dimensions and Scalars")
+            if isinstance(a, Array) and not a.is_dynamic and getattr(a, "offset", 0):
+                # the exported functions take the array's first element; an affine_offset in the descriptor would
+                # promise something the stub does not do
+                raise patterns.UnsupportedNestError("arrays with a non-zero offset are not supported as function arguments")
         target = source.target if isinstance(source, lang.Plan) else Target.HOST
+        if isinstance(source, lang.Plan):
+            source.check_launch_request()           # an impossible block is rejected here, as in lang/Plan.py:989-1004
         for f in self._fns.values():
             if not target.is_compatible_with(f.target):
                 raise NotImplementedError(
@@ -105,6 +112,11 @@ class Package:
         if name in self._fns:
             raise ValueError(f"function {name} already in package")
         fn = _PackagedFunction(name, base_name, spec, args, target, aux)
+        if isinstance(source, lang.Plan) and target.category is Target.Category.GPU:
+            try:
+                fn.launch_request = source.launch_request()
+            except ValueError:
+                fn.launch_request = None
         self._fns[name] = fn
         return fn
 
@@ -232,41 +244,91 @@ class Package:
         src_path = os.path.join(output_dir, f"{name}.cpp")
         with open(src_path, "w") as f:
             f.write(self._stub_source(name))
-        written = []
-        lib_name = ""
         cxx = shutil.which("g++") or shutil.which("c++")
         if cxx is None:
             raise RuntimeError("a host C++ compiler (g++) is required to build a package")
-        core_lib = os.path.join(_PKG_DIR, "libaccera_b200.so")
+        core_lib = os.path.join(_PKG_DIR, packaging.CORE_LIBRARY)
         if not os.path.exists(core_lib):
             from . import build as _build
             _build.build()
-        common = [cxx, "-O2", "-fPIC", "-std=c++17", f"-I{_INCLUDE_DIR}"]
-        if dynamic:
-            lib_name = f"{name}.so"
-            cmd = common + ["-shared", src_path, "-o", os.path.join(output_dir, lib_name), f"-L{_PKG_DIR}",
-                            "-laccera_b200", f"-Wl,-rpath,{_PKG_DIR}", "-Wl,-rpath,$ORIGIN"]
-            self._run(cmd)
-            written.append(os.path.join(output_dir, lib_name))
+
+        # 1. the object file, and a .hat that names it as its link target (Package.py:669-681)
+        obj_path = os.path.join(output_dir, f"{name}.o")
+        self._run([cxx, "-O2", "-fPIC", "-std=c++17", f"-I{_INCLUDE_DIR}", "-c", src_path, "-o", obj_path])
+        hat_path = os.path.join(output_dir, f"{name}.hat")
+        self._emit_header(name).Serialize(hat_path)
+
+        # 2. completed with what this layer knows, through the same calls the reference makes on hatlib's
+        #    HATFile (Package.py:678-764)
+        hf = hat_file.HATFile.Deserialize(hat_path)
+        hf.dependencies.link_target = os.path.basename(obj_path)
+        hf.dependencies.dynamic = [hat_file.LibraryReference(name="accera_b200", version="0.1", target_file=packaging.CORE_LIBRARY)]
+        for fn in self._fns.values():
+            hat_func = hf.function_map.get(fn.name)
+            if hat_func is None:
+                raise ValueError(f"Couldn't find header-declared function {fn.name} in emitted HAT file")
+            hat_func.auxiliary = dict(fn.auxiliary)
+            hat_func.auxiliary["accera_b200"] = self._kernel_metadata(fn)
+            if fn.target.category is Target.Category.GPU:
+                hf.target.required.gpu.model = fn.target.name
+        hf.target.required.os = hat_file.OperatingSystem.host()
+        hf.target.required.cpu.architecture = _platform.machine() or "x86_64"
+        hf.target.required.cpu.extensions = []
+        gpu = hf.target.required.gpu
+        gpu.runtime = "CUDA"
+        gpu.instruction_set_version = "sm_100a"
+        gpu.min_threads = 192
+        gpu.min_global_memory_KB = 0
+        gpu.min_shared_memory_KB = 227
+        gpu.min_texture_memory_KB = 0
+        hf.target.optimized_for.gpu.name = "NVIDIA B200"
+        hf.target.optimized_for.gpu.family = "Blackwell"
+        hf.target.optimized_for.gpu.cores = 148
+        hf.compiled_with.compiler = "nvcc + g++"
+        hf.compiled_with.flags = "-gencode arch=compute_100a,code=sm_100a -O3"
+        hf.compiled_with.libraries = [packaging.CORE_LIBRARY]
+        hf.description.author = self._description.get("author", "")
+        hf.description.version = self._description.get("version", "")
+        hf.description.license_url = self._description.get("license", "")
+        if self._description.get("auxiliary"):
+            hf.description.auxiliary = self._description["auxiliary"]
+        hf.Serialize(hat_path)
+
+        # 3. the library, and the .hat that points at it (Package.py:766-784)
+        written = [hat_path]
+        path_root = os.path.join(output_dir, name)
         if static:
-            obj = os.path.join(output_dir, f"{name}.o")
-            self._run(common + ["-c", src_path, "-o", obj])
-            lib_a = os.path.join(output_dir, f"{name}.a")
-            if os.path.exists(lib_a):
-                os.remove(lib_a)
-            self._run(["ar", "rcs", lib_a, obj])
-            os.remove(obj)
-            written.append(lib_a)
-            if not dynamic:
-                lib_name = f"{name}.a"
+            lib_hat_path = f"{path_root}_lib.hat"
+            packaging.create_static_package(hat_path, lib_hat_path)
+            os.replace(f"{path_root}_lib.a", f"{path_root}.a")
+            lib_hat_file = hat_file.HATFile.Deserialize(lib_hat_path)
+            lib_hat_file.dependencies.link_target = f"{name}.a"
+            lib_hat_file.dependencies.auxiliary["static"] = lib_hat_file.dependencies.link_target
+            lib_hat_file.Serialize()
+            static_hat = lib_hat_file
+            written.append(f"{path_root}.a")
+        if dynamic:
+            dyn_hat_path = f"{path_root}_dyn.hat"
+            packaging.create_dynamic_package(hat_path, dyn_hat_path)
+            os.replace(f"{path_root}_dyn.so", f"{path_root}.so")
+            dyn_hat_file = hat_file.HATFile.Deserialize(dyn_hat_path)
+            dyn_hat_file.dependencies.link_target = f"{name}.so"
+            dyn_hat_file.dependencies.auxiliary["dynamic"] = dyn_hat_file.dependencies.link_target
+            if static:
+                dyn_hat_file.dependencies.auxiliary["static"] = f"{name}.a"
+            dyn_hat_file.Serialize()
+            written.insert(1, f"{path_root}.so")
+        # the .hat a loader sees points at the dynamic library when there is one (Package.py:775-786 moves the
+        # static one over the original first, then the dynamic one)
+        if static:
+            shutil.move(f"{path_root}_lib.hat", hat_path)
+        if dynamic:
+            shutil.move(f"{path_root}_dyn.hat", hat_path)
+        os.remove(obj_path)
         if keep_source:
             written.append(src_path)
         else:
             os.remove(src_path)
-
-        hat_path = os.path.join(output_dir, f"{name}.hat")
-        self._hat_file(name, lib_name, dynamic).write(hat_path)
-        written.insert(0, hat_path)
         return written
 
     @staticmethod
@@ -276,48 +338,22 @@ class Package:
             raise RuntimeError(f"{' '.join(cmd)} failed:\n{r.stdout}\n{r.stderr}")
 
     # -------------------------------------------------------- .hat emission
-    def _hat_file(self, name: str, lib_name: str, dynamic: bool) -> hat_file.HATFile:
+    def _emit_header(self, name: str) -> hat_file.HATFile:
+        """The part of the .hat the reference's C++ layer writes (package_module.WriteHeader, Package.py:674-675;
+        TranslateToHeader.cpp:165-201, 402-506): one function table per public function and the C declarations."""
         hf = hat_file.HATFile(name=name)
-        desc = {"comment": "", "author": self._description.get("author", ""),
-                "version": self._description.get("version", ""), "license_url": self._description.get("license", "")}
-        if self._description.get("auxiliary"):
-            desc["auxiliary"] = self._description["auxiliary"]
-        hf.description = desc
         decl = [hat_file.header_prologue(name)]
         seen_alias = set()
         for fn in self._fns.values():
-            hfn = hat_file.Function(name=fn.name, description="", calling_convention="cdecl",
-                                    arguments=[self._parameter(fn, a) for a in fn.args],
-                                    auxiliary=dict(fn.auxiliary))
-            hfn.auxiliary["accera_b200"] = self._kernel_metadata(fn)
-            hf.functions.append(hfn)
-            if fn.target.category is Target.Category.GPU and fn.spec.kind == "gemm" and fn.spec.compute == "tensor":
-                # GPU targets: the host entry names the kernel it launches and a device-function entry carries
-                # the launch geometry (Package.py:726-743); here that kernel is the persistent tcgen05 GEMM
-                # precompiled in the core library: one 192-thread CTA per SM, ~193 KiB of dynamic shared memory
-                hfn.launches = fn.name + "__gpu__"
-                hfn.runtime = "CUDA"
-                hf.device_functions.append(hat_file.Function(
-                    name=fn.name + "__gpu__", description="", calling_convention="device",
-                    arguments=[self._parameter(fn, a) for a in fn.args], launch_parameters=[148, 1, 1, 192, 1, 1],
-                    dynamic_shared_mem_bytes=197888, provider="libaccera_b200.so", runtime="CUDA"))
+            hfn = hat_file.Function(name=fn.name, description="", calling_convention=hat_file.CallingConventionType.CDecl,
+                                    arguments=[self._parameter(fn, a) for a in fn.args])
+            hf.function_map[fn.name] = hfn
             decl.append(hfn.c_declaration() + "\n\n")
             if fn.base_name and fn.base_name not in seen_alias:
                 seen_alias.add(fn.base_name)
                 decl.append(hfn.c_alias(fn.base_name) + "\n")
         decl.append(hat_file.header_epilogue())
-        hf.declaration_code = "".join(decl)
-        hf.target = {
-            "required": {"os": "linux", "CPU": {"architecture": _platform.machine() or "x86_64", "extensions": []},
-                         "GPU": {"runtime": "CUDA", "instruction_set_version": "sm_100a", "min_threads": 192,
-                                 "min_global_memory_KB": 0, "min_shared_memory_KB": 227, "min_texture_memory_KB": 0}},
-            "optimized_for": {"GPU": {"name": "NVIDIA B200", "family": "Blackwell", "cores": 148}},
-        }
-        hf.dependencies = {"link_target": lib_name, "deploy_files": [],
-                           "dynamic": [{"name": "accera_b200", "version": "0.1", "target_file": "libaccera_b200.so"}],
-                           "auxiliary": {"dynamic" if dynamic else "static": lib_name}}
-        hf.compiled_with = {"compiler": "nvcc + g++", "flags": "-gencode arch=compute_100a,code=sm_100a -O3", "crt": "",
-                            "libraries": ["libaccera_b200.so"]}
+        hf.declaration.code = "".join(decl)
         return hf
 
     @staticmethod
@@ -343,10 +379,42 @@ class Package:
 
     @staticmethod
     def _kernel_metadata(fn: _PackagedFunction) -> Dict[str, Any]:
+        """What runs behind the exported function, for tools and readers; no loader needs it.
+
+        The reference lists a GPU function's kernel as a device function with `launches`, `launch_parameters` and
+        `dynamic_shared_mem_bytes`, and its loader compiles the `.cu` provider and launches that kernel itself
+        (Package.py:714-743).  The functions of this package are HOST-callable stubs over a prebuilt library: a
+        loader must call them like any CPU function (host arrays are staged through the GPU), so they carry no
+        `launches` link.  The geometry of the kernel the stub ends up launching is recorded here instead - the
+        true one for the tensor-core GEMM on the target's SM count (accb_gemm_launch_geometry), next to what a
+        bound plan asked for."""
         s = fn.spec
+        gpu_target = fn.target.category is Target.Category.GPU
         if s.kind == "gemm":
-            return {"op": "gemm", "compute": s.compute, "relu": s.relu, "bias": s.bias is not None,
-                    "alpha": float(s.alpha), "beta": float(s.beta)}
+            meta: Dict[str, Any] = {"op": "gemm", "compute": s.compute, "relu": s.relu, "bias": s.bias is not None,
+                                    "alpha": float(s.alpha), "beta": float(s.beta)}
+            static = all(isinstance(v, int) for v in (s.m, s.n, s.k)) and s.batch is None
+            if s.compute == "tensor" and static:
+                from . import runtime
+                in_type = s.a.element_type.name
+                try:
+                    sms = fn.target.num_sms or 148
+                    geo = runtime.gemm_launch_geometry(int(s.m), int(s.n), int(s.k), in_type=in_type, compute="tensor_preferred",
+                                                       num_sms=sms, b_row_major=not s.b_transposed and s.b.strides()[1] == 1)
+                    plan = runtime.gemm_tile_plan(int(s.m), int(s.n), int(s.k), in_type=in_type, compute="tensor_preferred",
+                                                  num_sms=sms, b_row_major=not s.b_transposed and s.b.strides()[1] == 1)
+                    meta.update({"kernel": "gemm_umma_kernel", "device_function": fn.name + "__gpu__",
+                                 "launch_parameters": geo["grid"] + geo["block"],
+                                 "dynamic_shared_mem_bytes": geo["dynamic_shared_mem_bytes"], "num_sms": sms,
+                                 "cta_pairs": plan["cta_pairs"], "tile_cols": plan["tile_cols"], "tiles": plan["tiles"]})
+                except Exception:            # the library is not built yet: the metadata is optional
+                    pass
+            if gpu_target and fn.launch_request is not None:
+                block, grid = fn.launch_request
+                meta["requested_launch_parameters"] = list(grid) + list(block)
+            if gpu_target:
+                meta["runtime"] = "CUDA"
+            return meta
         if s.kind == "reduce_mean":
             return {"op": "reduce_mean", "axes": list(s.axes), "keepdims": int(s.keepdims)}
         if s.kind == "gather":

@@ -428,22 +428,80 @@ def test_runtime_sized_matmul_and_reduce_mean_packages(tmp_path):
     assert "accb_reduce_mean_rank3(a2, INT64_C(1), a0, a1, a3, 4)" in src
 
 
-def test_gpu_target_functions_list_their_device_kernel(tmp_path):
-    # the reference adds a device-function entry and a `launches` link for GPU targets (Package.py:726-743)
+def test_gpu_target_functions_are_host_callable_and_record_the_true_launch(tmp_path):
+    # The reference lists a GPU function's kernel as a device function that its loader compiles from the `.cu`
+    # provider and launches itself (Package.py:714-743).  Here the exported function is a host-callable stub over a
+    # prebuilt library, so it must look like one to any loader: no `launches`, no device-function table.  What the
+    # stub ends up launching is recorded under auxiliary, from the library's own tile plan.
     nest, args = _gemm_nest(512, 512, 512, acc.ScalarType.float16, acc.ScalarType.float32, acc.Layout.LAST_MAJOR)
     plan = nest.create_schedule().create_plan(acc.Target(acc.Target.Model.NVIDIA_B200))
     plan.tensorize(indices=tuple(nest.get_indices()), mma_shape=acc.MMAShape.M16xN16xK16_B1)
     pkg = acc.Package()
     fn = pkg.add(plan, args=args, base_name="mm_gpu")
+    big_nest, big_args = _gemm_nest(65536, 8192, 8192, acc.ScalarType.bfloat16, acc.ScalarType.bfloat16, acc.Layout.LAST_MAJOR)
+    big_plan = big_nest.create_schedule().create_plan(acc.Target(acc.Target.Model.NVIDIA_B200))
+    big_plan.tensorize(indices=tuple(big_nest.get_indices()), mma_shape=acc.MMAShape.M16xN16xK16_B1)
+    big = pkg.add(big_plan, args=big_args, base_name="mm_big")
     hf = hat.HATFile.read(pkg.build("gpu_pkg", output_dir=str(tmp_path))[0])
-    host = hf.functions[0]
-    assert host.launches == fn.name + "__gpu__" and host.runtime == "CUDA"
-    dev = hf.device_functions[0]
-    assert dev.name == fn.name + "__gpu__" and dev.calling_convention == "device"
-    assert dev.launch_parameters[3:] == [192, 1, 1] and dev.dynamic_shared_mem_bytes > 190000
-    assert dev.provider == "libaccera_b200.so"
+    host = hf.function_map[fn.name]
+    assert host.launches is None and host.runtime is None and host.calling_convention == "cdecl"
+    assert hf.device_functions == [] and hf.device_function_map == {}
+    meta = host.auxiliary["accera_b200"]
+    assert meta["device_function"] == fn.name + "__gpu__" and meta["runtime"] == "CUDA" and meta["kernel"] == "gemm_umma_kernel"
+    want = runtime.gemm_launch_geometry(512, 512, 512, in_type="float16", compute="tensor_preferred")
+    assert meta["launch_parameters"] == want["grid"] + want["block"] and meta["launch_parameters"][3:] == [192, 1, 1]
+    assert meta["dynamic_shared_mem_bytes"] == want["dynamic_shared_mem_bytes"] > 190000
+    # the geometry is the variant's own: 16 single-CTA tiles of 128 columns here, 74 CTA pairs on the big problem
+    assert meta["launch_parameters"][0] == 16 and meta["tile_cols"] == 128 and meta["cta_pairs"] is False
+    bmeta = hf.function_map[big.name].auxiliary["accera_b200"]
+    assert bmeta["launch_parameters"][:3] == [148, 1, 1] and bmeta["cta_pairs"] is True and bmeta["tile_cols"] == 256
+    assert bmeta["tiles"] == 8192
+    assert hf.target.required.gpu.model == "NVidia B200" and hf.target.required.gpu.runtime == "CUDA"
     _, fns = hat.load(hf.path)
-    assert fns.names == [fn.name]                      # device functions are not host-callable
+    assert fns.names == [fn.name, big.name]
+
+
+def test_plan_bind_gives_the_reference_launch_geometry_and_rejects_what_it_rejects():
+    # the 4096^3 schedule with 64 x 64 block tiles and 16 x 16 warp tiles: grid 64 x 64, 16 warps (lang/Plan.py:879-956)
+    t = acc.Target(acc.Target.Model.NVIDIA_B200)
+
+    def build(block_tile, warp_tile, m=4096):
+        nest, args = _gemm_nest(m, m, m, acc.ScalarType.float16, acc.ScalarType.float32)
+        i, j, k = nest.get_indices()
+        s = nest.create_schedule()
+        ii, jj, kk = s.tile({i: block_tile, j: block_tile, k: 64})
+        iii, jjj, kkk = s.tile({ii: warp_tile, jj: warp_tile, kk: 16})
+        plan, tix = s._create_tensorizable_plan(t, block_indices=(i, j), warp_indices=(ii, jj), tensor_indices=(iii, jjj, kkk),
+                                                outer_nest_order=(i, j, k, ii, jj, kk))
+        plan.tensorize(indices=tix, mma_shape=acc.MMAShape.M16xN16xK16_B1)
+        return plan, args
+    plan, args = build(64, 16)
+    assert plan.launch_request() == ([128, 4, 1], [64, 64, 1])
+    pkg = acc.Package()
+    fn = pkg.add(plan, args=args, base_name="bound")
+    assert fn.launch_request == ([128, 4, 1], [64, 64, 1])
+    # 256 x 256 block tiles of 16 x 16 warp tiles: 16 x 16 warps = 8192 threads
+    bad, bad_args = build(256, 16)
+    with pytest.raises(ValueError, match="Invalid block size"):
+        acc.Package().add(bad, args=bad_args, base_name="too_big")
+    # thread bindings beyond the per-dimension limit
+    nest, args2 = _gemm_nest(4096, 4096, 64, acc.ScalarType.float32, acc.ScalarType.float32)
+    i, j, k = nest.get_indices()
+    s = nest.create_schedule()
+    ii = s.split(i, 2048)
+    p2 = s.create_plan(t)
+    p2.bind({i: t.GridUnit.BLOCK_X, ii: t.GridUnit.THREAD_X})
+    with pytest.raises(ValueError, match="Invalid block dimensions"):
+        acc.Package().add(p2, args=args2, base_name="too_wide")
+    # no bindings: 16 x 16 blocks following the split factors (lang/Plan.py:938-954)
+    nest3, _ = _gemm_nest(512, 256, 64, acc.ScalarType.float32, acc.ScalarType.float32)
+    i3, j3, k3 = nest3.get_indices()
+    s3 = nest3.create_schedule()
+    s3.split(i3, 32)
+    assert s3.create_plan(t).launch_request() == ([32, 16, 1], [16, 16, 1])
+    # CPU plans cannot be bound (lang/Plan.py:824-825)
+    with pytest.raises(ValueError, match="Only supported on plans with GPU targets"):
+        nest3.create_schedule().create_plan().bind({i3: t.GridUnit.BLOCK_X})
 
 
 def _batch_matmul_plan(batch, M, N, K, dtype=None, out_dtype=None, layouts=None, tensorize=True, epilogue_op=None):
@@ -673,3 +731,41 @@ def test_gemm_tile_plan_is_host_only_and_follows_the_cost_model():
     assert plan(8192, 8192, 8192, num_sms=132)["rounds"] == 16 and plan(8192, 8192, 8192, max_ctas=64)["rounds"] == 32
     with pytest.raises(runtime.AccbError):
         plan(0, 8, 8)
+
+
+def test_device_side_failures_are_attributed_to_the_launch_that_had_them():
+    # the status words a kernel writes, decoded as the library does (no GPU involved).  Words: [0] gather count,
+    # [1] GEMM site << 24 | block, [2] step, [3] id of the failing GEMM launch, [4] waits that ran out, [5] id of the
+    # gather launch that met a bad index.
+    ALL, GEMM, GATHER = 0, 1, 2
+    timeout = [0, (4 << 24) | 3, 7, 55, 2, 0, 0, 0]
+    code, msg = runtime.decode_status(timeout, GEMM, 55)
+    assert code == runtime.ERR_TIMEOUT and "epilogue waiting for the accumulator" in msg and "block 3, step 7" in msg and "launch 55" in msg
+    assert runtime.decode_status(timeout, GEMM, 56) == (0, "")          # a later GEMM call does not inherit it
+    assert runtime.decode_status(timeout, GATHER, 56) == (0, "")        # nor does a gather
+    assert runtime.decode_status(timeout, ALL, 0)[0] == runtime.ERR_TIMEOUT   # accb_synchronize reports it
+    code, msg = runtime.decode_status([0, (5 << 24) | 140, 12, 9, 1, 0, 0, 0], ALL)
+    assert code == runtime.ERR_TIMEOUT and "forwarding CTA waiting for a tile" in msg
+    bad_index = [3, 0, 0, 0, 0, 9, 0, 0]
+    assert runtime.decode_status(bad_index, GEMM, 10) == (0, "")        # a host-pointer GEMM is not blamed for an old gather
+    assert runtime.decode_status(bad_index, GATHER, 10) == (0, "")      # nor a later, clean gather
+    code, msg = runtime.decode_status(bad_index, GATHER, 9)
+    assert code == runtime.ERR_INDEX and "3 index value(s)" in msg
+    assert runtime.decode_status(bad_index, ALL)[0] == runtime.ERR_INDEX
+    assert runtime.decode_status([0] * 8, ALL) == (0, "")
+    # both recorded: the time-out is reported first, the index error stays for the next collection
+    both = [2, (1 << 24), 0, 4, 1, 6, 0, 0]
+    assert runtime.decode_status(both, ALL)[0] == runtime.ERR_TIMEOUT
+
+
+def test_options_are_validated_and_reset():
+    runtime.set_option("reset", 0)
+    assert runtime.gemm_tile_plan(4096, 4096, 4096)["tile_cols"] == 256
+    with runtime.options(**{"gemm.tile_cols": 128}):
+        assert runtime.gemm_tile_plan(4096, 4096, 4096)["tile_cols"] == 128
+    assert runtime.gemm_tile_plan(4096, 4096, 4096)["tile_cols"] == 256
+    for name, value in (("gemm.tile_cols", 192), ("gemm.pace_pct", 101), ("gemm.copy_ctas", 500), ("no.such.option", 1),
+                        ("gemm.wait_limit_us", -5), ("host_gemm.stage_chunks", 1000)):
+        with pytest.raises(runtime.AccbError):
+            runtime.set_option(name, value)
+    assert runtime.selected_device() == -1
