@@ -492,6 +492,7 @@ int accb_set_option(const char* name, int64_t value)
     else if (n == "gemm.test_drop_commit") o.gemm_test_drop_commit = v ? 1 : 0;
     else if (n == "gemm.verbose") o.gemm_verbose = v ? 1 : 0;
     else if (n == "host_gemm.stage_chunks") { if (v < 0 || v > 256) return fail(ACCB_ERR_ARG, "accb_set_option: host_gemm.stage_chunks is 0 (default) .. 256"); o.host_stage_chunks = v; }
+    else if (n == "reduce.rows_threads_per_output") { if (v != 0 && v != 32 && v != 64 && v != 128 && v != 256) return fail(ACCB_ERR_ARG, "accb_set_option: reduce.rows_threads_per_output is 0, 32, 64, 128 or 256"); o.reduce_rows_tpr = v; }
     else return fail(ACCB_ERR_ARG, "accb_set_option: unknown option " + n);
     return ACCB_OK;
 }

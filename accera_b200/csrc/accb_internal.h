@@ -46,6 +46,7 @@ struct Options {
     int gemm_test_drop_commit = 0;   // self-test: the MMA issuer leaves out the commit that completes the last accumulator
     int gemm_verbose = 0;            // print the launch plan to stderr
     int host_stage_chunks = 0;       // row chunks of the staged host-pointer GEMM (default 16)
+    int reduce_rows_tpr = 0;         // reduce_mean over contiguous segments: threads per output (32, 64, 128 or 256)
 };
 Options& options();
 
@@ -90,9 +91,17 @@ void gemm_umma_launch_geometry(const GemmLaunch& g, int want_two_sm, int32_t out
 // reduce_mean.cu
 // Scratch (fp32 partial sums) a launch needs for these dims, in bytes; 0 when the
 // single-pass kernels are used.
-size_t reduce_mean_scratch_bytes(int64_t d0, int64_t d1, int64_t d2, int axes_mask, int num_sms);
+// `cols_blocks_per_sm`: how many blocks per SM a strided (column) reduction is split into.  More blocks need more
+// partial sums and a longer second pass: 8 per SM was measured slower than 2 on every shape tried (4096 x 8192 over
+// the rows: 32.8 us against 30.3; 64 x 512 x 1024 over the middle axis: 30.7 against 22.8, because it starts to
+// split at all).  The entry point with the fixed built-in scratch depends on this number: keep the two in step.
+constexpr int kColsBlocksPerSm = 2;
+constexpr int kNoAllocColsBlocksPerSm = 2;
+size_t reduce_mean_scratch_bytes(int64_t d0, int64_t d1, int64_t d2, int axes_mask, int num_sms,
+                                 int cols_blocks_per_sm = kColsBlocksPerSm);
 int launch_reduce_mean(const float* data, int64_t d0, int64_t d1, int64_t d2, float* reduced, int axes_mask,
-                       float* scratch, size_t scratch_bytes, int num_sms, cudaStream_t stream, const char** err);
+                       float* scratch, size_t scratch_bytes, int num_sms, cudaStream_t stream, const char** err,
+                       int cols_blocks_per_sm = kColsBlocksPerSm);
 
 // gather.cu
 int launch_gather(const void* data, int64_t d0, int64_t d1, const int64_t* indices, int64_t i0, int64_t i1,

@@ -275,6 +275,7 @@ const char* accb_version(void);
  *                                                     ACCB_ERR_TIMEOUT (no fault, no trap; the context stays usable)
  *   "gemm.verbose"           0 | 1                    print the launch plan to stderr
  *   "host_gemm.stage_chunks" 0 (16) | 1..256          row chunks of the staged host-pointer GEMM
+ *   "reduce.rows_threads_per_output"  0 (choose) | 32 | 64 | 128 | 256   reduce_mean over contiguous segments
  */
 int accb_set_option(const char* name, int64_t value);
 
