@@ -40,7 +40,7 @@ WORKLOAD = "sharded bf16 GEMM+ReLU M=65536 N=8192 K=8192 (A row-major by M-row b
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel on one GPU's shard of this
 # workload, from ncu captures of `python -m accera_b200.profile_cases gemm_bf16 --m <rows per GPU>` (one capture per
 # shard size; a bench run cannot measure it itself, ncu has to replay the launch).  Keyed by (compute, GPUs).
-NCU_TRAFFIC_BYTES = {("tensor_2sm", 1): 12.74e9}
+NCU_TRAFFIC_BYTES = {("tensor_2sm", 1): 12.75e9, ("tensor_2sm", 2): 6.42e9, ("tensor_2sm", 4): 3.14e9, ("tensor_2sm", 8): 1.52e9}
 
 
 def load_peaks():
@@ -673,6 +673,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                          "peak": peak, "unit": "TFLOP/s", "frac": kernel_tflops / peak,
                          "frac_of_sustained_peak": (kernel_tflops / peaks["bf16_tflops_sustained"]) if peaks.get("bf16_tflops_sustained") else None,
                          "traffic": NCU_TRAFFIC_BYTES.get((compute, world)),
+                         "traffic_note": "ncu, one launch of this GPU's shard without replicas (DRAM bytes read + written)",
                          "nvlink_bytes_out_per_gpu_per_step": (world - 1) * plan.rows_per_rank * N * 2 if dist_on else 0,
                          "kernel": "gemm_umma_kernel<bf16,cta_group::2>" if compute == "tensor_2sm" else "gemm_umma_kernel<bf16>",
                          "per": "GPU", "peak_source": peaks["source"] + " burst bf16 (cuBLAS)"},
