@@ -490,6 +490,7 @@ int accb_set_option(const char* name, int64_t value)
     else if (n == "gemm.copy_ctas") { if (v > 128) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.copy_ctas is -1 (choose) or 0..128"); o.gemm_copy_ctas = v < 0 ? -1 : v; }
     else if (n == "gemm.wait_limit_us") { if (value < 0 || value > 10000000) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.wait_limit_us is 0 (default) .. 10000000"); o.gemm_wait_limit_us = v; }
     else if (n == "gemm.test_drop_commit") o.gemm_test_drop_commit = v ? 1 : 0;
+    else if (n == "gemm.pdl") o.gemm_pdl = v < 0 ? -1 : (v ? 1 : 0);
     else if (n == "gemm.verbose") o.gemm_verbose = v ? 1 : 0;
     else if (n == "host_gemm.stage_chunks") { if (v < 0 || v > 256) return fail(ACCB_ERR_ARG, "accb_set_option: host_gemm.stage_chunks is 0 (default) .. 256"); o.host_stage_chunks = v; }
     else if (n == "reduce.rows_threads_per_output") { if (v != 0 && v != 32 && v != 64 && v != 128 && v != 256) return fail(ACCB_ERR_ARG, "accb_set_option: reduce.rows_threads_per_output is 0, 32, 64, 128 or 256"); o.reduce_rows_tpr = v; }

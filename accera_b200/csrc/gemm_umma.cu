@@ -107,6 +107,7 @@ struct UmmaParams {
     int a_batched, b_batched;
     int64_t c_bs;
     int verbose;            // host only: print the launch plan to stderr
+    int pdl;                // host only: launch with programmatic stream serialization
     int launch_id;          // non-zero id of this launch: failures recorded in the status buffer carry it
     unsigned long long wait_ns;   // limit of every bounded wait, in nanoseconds of the global timer
     int drop_commit;        // self-test of the time-out path: the commit completing each CTA's last accumulator is left out
@@ -824,9 +825,15 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t rank = TWO_SM ? cluster_ctarank() : 0u;
     const bool leader = (rank == 0);
 
+    // Programmatic dependent launch: the next kernel of the stream may be scheduled onto free SMs now and run its
+    // own set-up (barriers, TMEM, descriptor prefetch) while this one computes; like this kernel below, it does not
+    // touch global memory before its griddepcontrol.wait, which returns once this whole grid has finished.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     // replicated GEMM with forwarding CTAs: the last copy_ctas CTAs (whole clusters) only move finished tiles
     const int compute_ctas = (int)gridDim.x - p.copy_ctas;
     if ((int)blockIdx.x >= compute_ctas) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         copy_tiles<TC, TWO_SM, BN>(p, cmaps, smem_base, smem_gen, (int)blockIdx.x - compute_ctas, p.copy_ctas);
         return;
     }
@@ -869,6 +876,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if constexpr (TWO_SM) cluster_sync_all(); else __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_holder;
+    // everything above touched only this CTA's shared memory and TMEM; from here on global memory is read and
+    // written, which must wait for the kernel before this one in the stream (a no-op for an ordinary launch)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int num_tiles = p.tiles_m * p.tiles_n * p.batch;
     const int num_units = compute_ctas / kCtas;
@@ -1229,11 +1239,20 @@ int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = Plan::kTotal;
     cfg.stream = g.stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
     if (TWO_SM) {
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr; cfg.numAttrs = 1;
+        attr[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
+        attr[cfg.numAttrs].val.clusterDim.x = 2; attr[cfg.numAttrs].val.clusterDim.y = 1; attr[cfg.numAttrs].val.clusterDim.z = 1;
+        ++cfg.numAttrs;
+    }
+    if (p.pdl) {
+        // let this launch be scheduled while the previous kernel of the stream is still running (see the kernel's
+        // griddepcontrol.wait): hides the launch and the set-up of back-to-back GEMMs
+        attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+        ++cfg.numAttrs;
     }
     // Per device and kernel variant, once: opt in to the large dynamic shared memory and find how many CTAs
     // (pairs) can be resident.  Both calls cost microseconds, which is the whole run time of a small GEMM.
@@ -1452,6 +1471,7 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
         p.verbose = o.gemm_verbose;
         p.wait_ns = o.gemm_wait_limit_us > 0 ? (unsigned long long)o.gemm_wait_limit_us * 1000ull : 1000000000ull;
         p.drop_commit = o.gemm_test_drop_commit ? 1 : 0;
+        p.pdl = o.gemm_pdl < 0 ? 1 : (o.gemm_pdl ? 1 : 0);
         // peers are written with register stores unless the caller asks for TMA stores or a row's last vector is partial
         const bool vec_rows = ((d.n * elem_size(d.c_type)) % 16) == 0;
         p.peer_store = (g.n_extra_c > 0 && vec_rows && (o.gemm_peer_store < 0 ? kPeerStoreDefault : o.gemm_peer_store)) ? 1 : 0;

@@ -273,6 +273,8 @@ const char* accb_version(void);
  *   "gemm.test_drop_commit"  0 | 1                    self-test: each CTA's last accumulator is never signalled complete,
  *                                                     so the epilogue's bounded wait runs out and the launch reports
  *                                                     ACCB_ERR_TIMEOUT (no fault, no trap; the context stays usable)
+ *   "gemm.pdl"               -1 (on) | 0 | 1          programmatic dependent launch: the next GEMM of a stream is scheduled
+ *                                                     and sets itself up while the previous kernel still runs
  *   "gemm.verbose"           0 | 1                    print the launch plan to stderr
  *   "host_gemm.stage_chunks" 0 (16) | 1..256          row chunks of the staged host-pointer GEMM
  *   "reduce.rows_threads_per_output"  0 (choose) | 32 | 64 | 128 | 256   reduce_mean over contiguous segments
