@@ -213,7 +213,7 @@ size_t type_bytes(int t)
 {
     switch (t) {
     case ACCB_F32: case ACCB_S32: return 4;
-    case ACCB_F16: case ACCB_BF16: return 2;
+    case ACCB_F16: case ACCB_BF16: case ACCB_S16: return 2;
     case ACCB_S8: case ACCB_U8: return 1;
     default: return 0;
     }

@@ -39,6 +39,7 @@ template <> __device__ __forceinline__ float widen<float, __half>(__half v) { re
 template <> __device__ __forceinline__ float widen<float, __nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ int widen<int, int8_t>(int8_t v) { return (int)v; }
 template <> __device__ __forceinline__ int widen<int, uint8_t>(uint8_t v) { return (int)v; }
+template <> __device__ __forceinline__ int widen<int, int16_t>(int16_t v) { return (int)v; }
 
 template <typename T>
 __device__ __forceinline__ T narrow(float v);
@@ -691,6 +692,10 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err)
     } else if (a == ACCB_U8 && b == ACCB_U8 && c == ACCB_S32) {
         if (d.alpha != 1.0f || (d.beta != 0.0f && d.beta != 1.0f) || g.bias) { *err = "integer GEMM supports alpha=1, beta in {0,1}, no bias"; return ACCB_ERR_ARG; }
         e = launch_typed<uint8_t, uint8_t, int32_t, int>(g, p);
+    } else if (a == ACCB_S16 && b == ACCB_S16 && c == ACCB_S32) {
+        // the reference's int16 matmul (accera/python/accera/test/int_matmul_tests.py:40-68): exact int32 accumulation
+        if (d.alpha != 1.0f || (d.beta != 0.0f && d.beta != 1.0f) || g.bias) { *err = "integer GEMM supports alpha=1, beta in {0,1}, no bias"; return ACCB_ERR_ARG; }
+        e = launch_typed<int16_t, int16_t, int32_t, int>(g, p);
     } else {
         *err = "unsupported GEMM element-type combination";
         return ACCB_ERR_ARG;

@@ -1148,7 +1148,7 @@ int elem_size(int t)
 {
     switch (t) {
     case ACCB_F32: case ACCB_S32: return 4;
-    case ACCB_F16: case ACCB_BF16: return 2;
+    case ACCB_F16: case ACCB_BF16: case ACCB_S16: return 2;
     default: return 1;
     }
 }

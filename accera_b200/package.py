@@ -32,7 +32,7 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 _INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
 
 _ACCB_TYPE = {ScalarType.float32: "ACCB_F32", ScalarType.float16: "ACCB_F16", ScalarType.bfloat16: "ACCB_BF16",
-              ScalarType.int8: "ACCB_S8", ScalarType.int32: "ACCB_S32", ScalarType.uint8: "ACCB_U8"}
+              ScalarType.int8: "ACCB_S8", ScalarType.int32: "ACCB_S32", ScalarType.uint8: "ACCB_U8", ScalarType.int16: "ACCB_S16"}
 _COMPUTE = {"auto": "ACCB_COMPUTE_AUTO", "simt": "ACCB_COMPUTE_SIMT", "tensor": "ACCB_COMPUTE_TENSOR_PREFERRED"}
 
 
@@ -157,7 +157,7 @@ class Package:
             ok = {(ScalarType.float32,) * 3, (ScalarType.float16, ScalarType.float16, ScalarType.float32),
                   (ScalarType.float16,) * 3, (ScalarType.bfloat16, ScalarType.bfloat16, ScalarType.float32),
                   (ScalarType.bfloat16,) * 3, (ScalarType.int8, ScalarType.int8, ScalarType.int32),
-                  (ScalarType.uint8, ScalarType.uint8, ScalarType.int32)}
+                  (ScalarType.uint8, ScalarType.uint8, ScalarType.int32), (ScalarType.int16, ScalarType.int16, ScalarType.int32)}
             if key not in ok:
                 raise patterns.UnsupportedNestError(f"unsupported GEMM element types {[k.name for k in key]}")
             if spec.bias is not None and spec.bias.element_type is not ScalarType.float32:

@@ -20,13 +20,13 @@ import numpy as np
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libaccera_b200.so")
 
-F32, F16, BF16, S8, S32, U8 = 0, 1, 2, 3, 4, 5
+F32, F16, BF16, S8, S32, U8, S16 = 0, 1, 2, 3, 4, 5, 6
 COMPUTE_AUTO, COMPUTE_SIMT, COMPUTE_TENSOR, COMPUTE_TENSOR_2SM, COMPUTE_TENSOR_PREFERRED = 0, 1, 2, 3, 4
 EPI_NONE, EPI_RELU = 0, 1
 ERR_ARG, ERR_CUDA, ERR_INDEX, ERR_TIMEOUT, ERR_LIMIT = -1, -2, -3, -4, -5
 
-TYPE_BYTES = {F32: 4, F16: 2, BF16: 2, S8: 1, S32: 4, U8: 1}
-_NP_TYPE = {"float32": F32, "float16": F16, "int8": S8, "int32": S32, "uint8": U8}
+TYPE_BYTES = {F32: 4, F16: 2, BF16: 2, S8: 1, S32: 4, U8: 1, S16: 2}
+_NP_TYPE = {"float32": F32, "float16": F16, "int8": S8, "int32": S32, "uint8": U8, "int16": S16}
 _COMPUTE = {"auto": COMPUTE_AUTO, "simt": COMPUTE_SIMT, "tensor": COMPUTE_TENSOR, "tensor_2sm": COMPUTE_TENSOR_2SM,
             "tensor_preferred": COMPUTE_TENSOR_PREFERRED}
 
@@ -204,9 +204,9 @@ def _describe(x, kind: Optional[str] = None):
     if _is_torch(x):
         import torch
         tmap = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int8: S8, torch.int32: S32,
-                torch.uint8: U8}
+                torch.uint8: U8, torch.int16: S16}
         if kind is not None:
-            code = {"bfloat16": BF16, "float16": F16, "float32": F32, "int8": S8, "uint8": U8, "int32": S32}[kind]
+            code = {"bfloat16": BF16, "float16": F16, "float32": F32, "int8": S8, "uint8": U8, "int32": S32, "int16": S16}[kind]
         elif x.dtype in tmap:
             code = tmap[x.dtype]
         elif x.dtype == torch.int64:

@@ -36,13 +36,14 @@ enum {
     ACCB_BF16 = 2,
     ACCB_S8 = 3,
     ACCB_S32 = 4,
-    ACCB_U8 = 5
+    ACCB_U8 = 5,
+    ACCB_S16 = 6   /* int16 inputs accumulate exactly into int32 on the CUDA cores (no tensor-core path) */
 };
 
 /* how a GEMM is computed */
 enum {
     ACCB_COMPUTE_AUTO = 0,   /* tensor cores for f16/bf16/s8/u8 inputs, fp32 SIMT for f32 inputs */
-    ACCB_COMPUTE_SIMT = 1,   /* CUDA-core FMA in fp32 / int32: bit-faithful fp32 */
+    ACCB_COMPUTE_SIMT = 1,   /* CUDA-core FMA in fp32 / int32: bit-faithful fp32; the only path for int16 inputs */
     ACCB_COMPUTE_TENSOR = 2, /* tcgen05: f16/bf16 -> f32, s8/u8 -> s32, f32 inputs as TF32 */
     ACCB_COMPUTE_TENSOR_2SM = 3, /* tcgen05 with CTA pairs (cta_group::2); same numerics as TENSOR */
     ACCB_COMPUTE_TENSOR_PREFERRED = 4 /* tcgen05 when the operand layout allows it (K-contiguous A and B,

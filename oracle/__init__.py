@@ -25,10 +25,10 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
-F32, F16, BF16, S8, S32, U8 = 0, 1, 2, 3, 4, 5
+F32, F16, BF16, S8, S32, U8, S16 = 0, 1, 2, 3, 4, 5, 6
 EPI_NONE, EPI_RELU = 0, 1
 
-_KIND_OF = {"float32": F32, "float16": F16, "bfloat16": BF16, "int8": S8, "int32": S32, "uint8": U8}
+_KIND_OF = {"float32": F32, "float16": F16, "bfloat16": BF16, "int8": S8, "int32": S32, "uint8": U8, "int16": S16}
 
 
 def build(force: bool = False) -> None:
@@ -126,7 +126,7 @@ def gemm(A: np.ndarray, B: np.ndarray, C: np.ndarray, *, in_kind: str = None, ou
     if threads is not None:
         L.orc_set_threads(int(threads))
     m0, m1 = rows if rows is not None else (0, M)
-    if in_kind in ("int8", "uint8"):
+    if in_kind in ("int8", "uint8", "int16"):
         assert out_kind == "int32" and alpha == 1.0 and beta in (0.0, 1.0) and bias is None
         sa, sb, sc = _elem_strides(A), _elem_strides(B), _elem_strides(C)
         L.orc_gemm_int8(A.ctypes.data, B.ctypes.data, C.ctypes.data, _KIND_OF[in_kind], _KIND_OF[in_kind],

@@ -52,7 +52,7 @@
 #endif
 
 /* element kinds shared with the Python wrapper */
-enum { ORC_F32 = 0, ORC_F16 = 1, ORC_BF16 = 2, ORC_S8 = 3, ORC_S32 = 4, ORC_U8 = 5 };
+enum { ORC_F32 = 0, ORC_F16 = 1, ORC_BF16 = 2, ORC_S8 = 3, ORC_S32 = 4, ORC_U8 = 5, ORC_S16 = 6 };
 
 /* epilogue flags */
 enum { ORC_EPI_NONE = 0, ORC_EPI_RELU = 1 };
@@ -217,9 +217,12 @@ void orc_gemm_int8(const void* A, const void* B, int32_t* C,
                 for (int64_t k = 0; k < K; ++k) acc += (int32_t)a[k] * (int32_t)b[k];
             } else
             for (int64_t k = 0; k < K; ++k) {
-                int32_t a = (a_kind == ORC_U8) ? (int32_t)((const uint8_t*)A)[i * sa0 + k * sa1]
+                /* int16 operands: cast(a, int32) * cast(b, int32), accera/python/accera/test/int_matmul_tests.py:55 */
+                int32_t a = (a_kind == ORC_S16) ? (int32_t)((const int16_t*)A)[i * sa0 + k * sa1]
+                          : (a_kind == ORC_U8) ? (int32_t)((const uint8_t*)A)[i * sa0 + k * sa1]
                                                : (int32_t)((const int8_t*)A)[i * sa0 + k * sa1];
-                int32_t b = (b_kind == ORC_U8) ? (int32_t)((const uint8_t*)B)[k * sb0 + j * sb1]
+                int32_t b = (b_kind == ORC_S16) ? (int32_t)((const int16_t*)B)[k * sb0 + j * sb1]
+                          : (b_kind == ORC_U8) ? (int32_t)((const uint8_t*)B)[k * sb0 + j * sb1]
                                                : (int32_t)((const int8_t*)B)[k * sb0 + j * sb1];
                 acc += a * b;
             }

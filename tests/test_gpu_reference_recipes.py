@@ -402,3 +402,35 @@ def test_a_stale_gather_error_is_not_blamed_on_a_later_call():
     assert ei.value.code == rt.ERR_INDEX
     assert out[1].abs().sum().item() == 0.0 and out[0].reshape(-1).tolist() == [12.0, 13.0, 14.0, 15.0]
     rt.synchronize()
+
+
+# ---------------------------------------------------------------------------
+# the reference's int16 matmul test (accera/python/accera/test/int_matmul_tests.py:40-68)
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("m,n,k", [(1, 8, 2), (4, 16, 64), (100, 72, 515)])
+def test_reference_int16_matmul_recipe(tmp_path, m, n, k):
+    # C[i, j] += cast(A[i, k], int32) * cast(B[j, k], int32) with B stored [N, K]; inputs from {0..99}; the reference
+    # compares with (A @ B.T).astype(int32) exactly
+    A = acc.Array(role=acc.Role.INPUT, element_type=acc.ScalarType.int16, shape=(m, k))
+    B = acc.Array(role=acc.Role.INPUT, element_type=acc.ScalarType.int16, shape=(n, k))
+    C = acc.Array(role=acc.Role.INPUT_OUTPUT, element_type=acc.ScalarType.int32, shape=(m, n))
+    nest = acc.Nest((m, n, k))
+    i, j, kk = nest.get_indices()
+
+    @nest.iteration_logic
+    def _():
+        C[i, j] += acc.cast(A[i, kk], acc.ScalarType.int32) * acc.cast(B[j, kk], acc.ScalarType.int32)
+    pkg = acc.Package()
+    fn = pkg.add(nest.create_schedule(), args=(A, B, C), base_name="test_int16_matmul")
+    _, fns = hat.load(pkg.build("int16_pkg", output_dir=str(tmp_path))[0])
+    rng = np.random.default_rng(m + n)
+    a = rng.integers(0, 100, (m, k)).astype(np.int16)
+    b = rng.integers(0, 100, (n, k)).astype(np.int16)
+    c = np.zeros((m, n), np.int32)
+    c_ref = (a.astype(np.int32) @ b.astype(np.int32).transpose()).astype(np.int32)
+    fns[fn.name](a, b, c)
+    assert np.array_equal(c, c_ref)
+    assert np.array_equal(c, oracle.gemm(a, b.T, np.zeros((m, n), np.int32)))
+    fns[fn.name](a, b, c)                            # C is INPUT_OUTPUT: a second call accumulates
+    assert np.array_equal(c, 2 * c_ref)

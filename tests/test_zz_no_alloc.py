@@ -83,3 +83,64 @@ def test_noalloc_rejects_host_buffers_and_bad_arguments():
     assert rc == rt.ERR_ARG and b"device memory" in lib.accb_last_error()
     assert lib.accb_reduce_mean_rank3_noalloc(None, 1, 2, 3, None, 9, None) == rt.ERR_ARG
     assert lib.accb_reduce_mean_rank3_noalloc(None, -1, 2, 3, None, 4, None) == rt.ERR_ARG
+
+
+def test_noalloc_leaves_free_device_memory_unchanged():
+    """The contract in the name: once the first call on the device has resolved the built-in array's address, a call
+    changes nothing about device memory - not the driver's free-memory figure, and not the cached scratch buffer of
+    the ordinary entry point."""
+    import torch
+    dev = torch.device("cuda:0")
+    x = torch.randn(1, 4, 1 << 20, device=dev)
+    y = torch.empty(4, device=dev)
+    y2 = torch.empty(1 << 14, device=dev)
+    x2 = torch.randn(3000, 1, 1 << 14, device=dev)
+    lib = rt.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream or None)
+
+    def call(data, out, d, mask):
+        rc = lib.accb_reduce_mean_rank3_noalloc(ctypes.c_void_p(data.data_ptr()), d[0], d[1], d[2], ctypes.c_void_p(out.data_ptr()), mask, stream)
+        assert rc == 0, lib.accb_last_error().decode()
+    call(x, y, (1, 4, 1 << 20), 4)                     # set-up call (first use on this device resolves the symbol)
+    torch.cuda.synchronize(dev)
+    rt.release_workspace()                             # the ordinary entry point's cached buffers are gone: nothing to lean on
+    torch.cuda.synchronize(dev)
+    free_before, _ = torch.cuda.mem_get_info(dev)
+    call(x, y, (1, 4, 1 << 20), 4)                     # rows split: uses the built-in scratch
+    call(x2, y2, (3000, 1, 1 << 14), 1)                # cols split: uses it again, over the leftovers
+    torch.cuda.synchronize(dev)
+    free_after, _ = torch.cuda.mem_get_info(dev)
+    assert free_after == free_before
+    assert (y - x.double().mean(dim=(0, 2)).float()).abs().max().item() <= 1e-5 * x.abs().mean().item()
+    assert lib.accb_last_error() == b""                # a successful call leaves no stale error text behind
+
+
+def test_noalloc_works_in_a_process_that_never_used_the_allocating_entry_point():
+    """A fresh process calls only the no-alloc entry point (two shapes that take the split path) and checks the
+    result itself: it cannot be borrowing scratch memory that accb_reduce_mean_rank3 allocated earlier."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = r'''
+import ctypes, sys
+sys.path.insert(0, %r)
+import torch
+from accera_b200 import runtime as rt
+dev = torch.device("cuda:0")
+lib = rt.lib()
+torch.manual_seed(3)
+for shape, mask, dims in (((1, 4, 1 << 20), 4, (0, 2)), ((6000, 1, 192), 1, (0,))):
+    x = torch.randn(*shape, device=dev)
+    n_out = 4 if mask == 4 else 192
+    y = torch.full((n_out,), float("nan"), device=dev)
+    rc = lib.accb_reduce_mean_rank3_noalloc(ctypes.c_void_p(x.data_ptr()), shape[0], shape[1], shape[2],
+                                            ctypes.c_void_p(y.data_ptr()), mask, None)
+    assert rc == 0, lib.accb_last_error()
+    torch.cuda.synchronize()
+    want = x.double().mean(dim=dims).reshape(-1).float()
+    assert (y - want).abs().max().item() <= 1e-5 * x.abs().mean().item(), shape
+print("fresh process ok")
+''' % root
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "fresh process ok" in r.stdout, r.stdout + r.stderr
