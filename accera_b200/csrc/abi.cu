@@ -234,6 +234,146 @@ int selected_device(int* dev) { return current_device(dev); }
 
 namespace {
 
+int tensor_gemm_split_k(const GemmLaunch& g, const char** err);
+
+// An operand the tensor-core path cannot take only because its rows (or its base) are not 16-byte aligned - a
+// K of 30522 bf16 elements, say - is copied into a temporary with an aligned pitch (one pitched device-to-device
+// copy; rows past the matrix edge need no padding, TMA zero-fills them) and the GEMM runs on that.  The temporary comes
+// from the stream-ordered allocator (cudaMallocAsync on the launch stream, freed on it right after the launch), so
+// nothing synchronises and concurrent streams do not share it.  Returns launches made, 0 when this does not apply
+// (the caller then uses the CUDA-core kernel), or a negative ACCB_ERR_*.
+int tensor_gemm_with_repacked_operands(const GemmLaunch& g0, const char** err)
+{
+    const accb_gemm_desc& d0 = g0.d;
+    if (g0.batch > 1 || g0.n_extra_c > 0 || d0.k <= 0 || !gemm_umma_types_supported(d0)) return 0;
+    if ((double)d0.m * (double)d0.n * (double)d0.k < (double)(1 << 24)) return 0;      // too small to pay for two more operations
+    GemmLaunch g = g0;
+    accb_gemm_desc& d = g.d;
+    const size_t es = type_bytes(d.a_type);
+    if (es == 0 || type_bytes(d.b_type) != es) return 0;
+    // how each operand lies in memory: `rows` runs of `width` contiguous elements, `pitch` elements apart;
+    // k_is_width: the contiguous direction is K
+    struct Op { const void** base; int64_t* pitch; int64_t rows, width; bool k_is_width, aligned; };
+    Op ops[2];
+    auto describe = [&](Op& o, const void** base, int64_t* stride, int64_t dim0, int64_t dim1, bool k_is_dim1) {
+        // the array is dim0 x dim1 with element strides stride[0], stride[1]; one of them must be 1
+        if (stride[1] == 1) { o.rows = dim0; o.width = dim1; o.pitch = &stride[0]; o.k_is_width = k_is_dim1; }
+        else if (stride[0] == 1) { o.rows = dim1; o.width = dim0; o.pitch = &stride[1]; o.k_is_width = !k_is_dim1; }
+        else return false;
+        o.base = base;
+        o.aligned = ((*o.pitch * (int64_t)es) % 16 == 0) && ((reinterpret_cast<uintptr_t>(*base) & 15) == 0);
+        return true;
+    };
+    if (!describe(ops[0], &g.a, d.a_stride, d.m, d.k, true) || !describe(ops[1], &g.b, d.b_stride, d.k, d.n, false)) return 0;
+    if (ops[0].aligned && ops[1].aligned) return 0;             // alignment is not what keeps it off the tensor cores
+    // A long K is padded with zeros to a multiple of 512 while the operands are copied anyway, so that it divides
+    // into equal, aligned slices for the K-split below (30522 has no such divisor, 30720 has plenty).
+    const int64_t k_new = (d.k >= 4096 && d.k % 512 != 0) ? (d.k + 511) / 512 * 512 : d.k;
+    void* tmp[2] = { nullptr, nullptr };
+    auto release = [&]() { for (void* t : tmp) if (t) cudaFreeAsync(t, g.stream); };
+    for (int i = 0; i < 2; ++i) {
+        Op& o = ops[i];
+        if (o.aligned && k_new == d.k) continue;
+        const int64_t new_rows = o.k_is_width ? o.rows : k_new;              // K-rows operands get zero rows appended
+        const int64_t new_width = o.k_is_width ? k_new : o.width;            // K-contiguous ones get zero columns
+        const int64_t old_rows = o.k_is_width ? o.rows : d.k;
+        const int64_t old_width = o.k_is_width ? d.k : o.width;
+        const size_t new_pitch = ((size_t)new_width * es + 15) & ~(size_t)15;
+        cudaError_t e = cudaMallocAsync(&tmp[i], new_pitch * (size_t)new_rows, g.stream);
+        if (e != cudaSuccess) { (void)cudaGetLastError(); tmp[i] = nullptr; release(); return 0; }   // no memory to spare: CUDA-core kernel
+        if (k_new != d.k) e = cudaMemsetAsync(tmp[i], 0, new_pitch * (size_t)new_rows, g.stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(tmp[i], new_pitch, *o.base, (size_t)*o.pitch * es, (size_t)old_width * es, (size_t)old_rows,
+                                  cudaMemcpyDeviceToDevice, g.stream);
+        if (e != cudaSuccess) { *err = cudaGetErrorString(e); release(); return ACCB_ERR_CUDA; }
+        *o.base = tmp[i];
+        *o.pitch = (int64_t)(new_pitch / es);
+    }
+    d.k = k_new;
+    const char* why = nullptr;
+    int n = 0;
+    if (gemm_umma_supported(g, &why)) {
+        n = tensor_gemm_split_k(g, err);
+        if (n == 0) n = launch_gemm_umma(g, d.m > 128 ? -1 : 0, err);
+    }
+    release();
+    if (n > 0) note_launches(2);
+    return n;
+}
+
+// A problem with few output tiles and a long K (1024 x 2048 x 30528: 32 tiles for 74 CTA pairs, 477 K steps each)
+// is cut along K into `slices` equal parts that run as ONE batched launch - slice s is "problem" s, reading
+// A[:, s*k/S ...] and B[s*k/S ..., :] in place through the batched kernel's rank-3 tensor maps and writing an fp32
+// (int32) partial result - followed by one streaming pass that adds the partials in slice order and applies the
+// epilogue (deterministic: no atomics, the same bits on every run).  The partials live in a stream-ordered temporary.
+// Returns launches made, 0 when splitting does not apply, or a negative ACCB_ERR_*.
+int tensor_gemm_split_k(const GemmLaunch& g, const char** err)
+{
+    const accb_gemm_desc& d = g.d;
+    if (g.batch > 1 || g.n_extra_c > 0 || d.k < 2048) return 0;
+    const size_t es = type_bytes(d.a_type);
+    const double slab = 128.0 / (double)es;                 // K elements per pipeline stage
+    // Two tilings are candidates: the one the launch code would pick for the unsplit problem, and the widest tile
+    // (256 columns; a CTA pair when M spans more than one tile row).  For each, the largest slice count that fills
+    // the machine, divides K exactly (a slice must not run into the next row of a K-contiguous operand), keeps
+    // every slice's start 16-byte aligned and leaves each slice at least 512 long.  Costs in microseconds from the
+    // measured stage times: 0.28 us per stage of a 256-column tile, 0.22 us of a 128-column one; the split adds a
+    // second launch and the partials' round trip through HBM (about 7 us + bytes at 4 TB/s).
+    int plan_two = 0, plan_cols = 0;
+    int64_t plan_tiles = 0, plan_rounds = 0;
+    gemm_umma_tile_plan(g, d.m > 128 ? -1 : 0, &plan_two, &plan_cols, &plan_tiles, &plan_rounds);
+    struct Cand { int two_sm, cols; };
+    const Cand cands[2] = { { plan_two, plan_cols }, { d.m > 128 ? 1 : 0, 256 } };
+    const double unsplit_us = (double)plan_rounds * ((double)d.k / slab) * (plan_cols == 256 ? 0.28 : 0.22);
+    double best_us = unsplit_us;
+    int best_slices = 1;
+    Cand best = cands[0];
+    for (const Cand& c : cands) {
+        const int64_t rows = c.two_sm ? 256 : 128;
+        const int64_t tiles = ((d.m + rows - 1) / rows) * ((d.n + c.cols - 1) / c.cols);
+        const int64_t units = c.two_sm ? g.num_sms / 2 : g.num_sms;
+        for (int64_t sl = units / tiles < 16 ? units / tiles : 16; sl >= 2; --sl) {
+            if (d.k % sl != 0) continue;
+            const int64_t ks = d.k / sl;
+            if (ks < 512 || (ks * (int64_t)es) % 16 != 0) continue;
+            const double rounds = (double)((tiles * sl + units - 1) / units);
+            const double us = rounds * ((double)ks / slab) * (c.cols == 256 ? 0.28 : 0.22) + 7.0 +
+                              (double)(sl + 1) * (double)d.m * (double)d.n * 4.0 / 4.0e6;
+            if (us < best_us * 0.9) { best_us = us; best_slices = (int)sl; best = c; }
+            break;                                          // fewer slices of this tiling only cost more
+        }
+    }
+    if (best_slices < 2) return 0;
+    const int slices = best_slices;
+    const int64_t ks = d.k / slices;
+    const bool integer = d.c_type == ACCB_S32;
+    void* ws = nullptr;
+    cudaError_t e = cudaMallocAsync(&ws, (size_t)slices * (size_t)d.m * (size_t)d.n * 4, g.stream);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return 0; }     // no memory to spare: unsplit launch
+    GemmLaunch part = g;
+    part.d.k = ks;
+    part.d.c_type = integer ? ACCB_S32 : ACCB_F32;
+    part.d.c_stride[0] = d.n; part.d.c_stride[1] = 1;
+    part.d.alpha = 1.0f; part.d.beta = 0.0f;
+    part.d.epilogue = ACCB_EPI_NONE;
+    part.bias = nullptr;
+    part.c = ws;
+    part.batch = slices;
+    part.a_batch_stride = ks * d.a_stride[1];
+    part.b_batch_stride = ks * d.b_stride[0];
+    part.c_batch_stride = d.m * d.n;
+    part.force_tile_cols = best.cols;
+    const char* why = nullptr;
+    int n = 0;
+    if (gemm_umma_supported(part, &why)) n = launch_gemm_umma(part, best.two_sm, err);
+    if (n > 0) {
+        const int r = launch_splitk_reduce(ws, slices, d, g.c, g.bias, g.stream, err);
+        n = r < 0 ? r : n + r;
+    }
+    cudaFreeAsync(ws, g.stream);
+    return n;
+}
+
 // Picks the kernel for one GEMM on device pointers.  Returns launches made or a negative ACCB_ERR_*.
 int dispatch_gemm(const GemmLaunch& g, const char** err)
 {
@@ -242,15 +382,19 @@ int dispatch_gemm(const GemmLaunch& g, const char** err)
     if (d.compute == ACCB_COMPUTE_SIMT) return launch_gemm_simt(g, err);
     if (d.compute == ACCB_COMPUTE_TENSOR) return launch_gemm_umma(g, 0, err);
     if (d.compute == ACCB_COMPUTE_TENSOR_2SM) return launch_gemm_umma(g, 1, err);
-    if (d.compute == ACCB_COMPUTE_TENSOR_PREFERRED) {
+    // TENSOR_PREFERRED: the tensor cores whenever the element types have a tensor-core form - directly when the
+    // layout allows it, through an aligned copy of an operand whose rows are not 16-byte aligned, and the CUDA-core
+    // kernel for what is left (general strides, M / N-contiguous fp32).
+    // AUTO: the same, except that fp32 inputs stay on the bit-faithful fp32 path.
+    if (d.compute == ACCB_COMPUTE_TENSOR_PREFERRED || d.a_type != ACCB_F32) {
         const char* why = nullptr;
-        if (gemm_umma_supported(g, &why)) return launch_gemm_umma(g, d.m > 128 ? -1 : 0, err);
-        return launch_gemm_simt(g, err);
+        if (gemm_umma_supported(g, &why)) {
+            const int n = tensor_gemm_split_k(g, err);
+            return n != 0 ? n : launch_gemm_umma(g, d.m > 128 ? -1 : 0, err);
+        }
+        const int n = tensor_gemm_with_repacked_operands(g, err);
+        if (n != 0) return n;
     }
-    // AUTO: fp32 inputs stay on the bit-faithful fp32 path; narrower inputs take the tensor cores when the
-    // layout allows it (CTA pairs as soon as there is more than one 128-row tile) and the SIMT kernel otherwise
-    const char* why = nullptr;
-    if (d.a_type != ACCB_F32 && gemm_umma_supported(g, &why)) return launch_gemm_umma(g, d.m > 128 ? -1 : 0, err);
     return launch_gemm_simt(g, err);
 }
 

@@ -69,6 +69,7 @@ struct GemmLaunch {
     // b * *_batch_stride elements after the base (a stride of 0 shares that operand between all problems)
     int64_t batch = 1;
     int64_t a_batch_stride = 0, b_batch_stride = 0, c_batch_stride = 0;
+    int force_tile_cols = 0;   // tensor-core path: 128 or 256 accumulator columns per tile instead of the cost model's choice
     cudaStream_t stream;
     int* status;       // device pointer to kStatusWords ints
     int launch_id;     // attribution of device-side failures (next_launch_id)
@@ -81,6 +82,7 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err);
 
 // gemm_umma.cu: tcgen05/TMEM path. `supported` explains in *why when it returns false.
 bool gemm_umma_supported(const GemmLaunch& g, const char** why);
+bool gemm_umma_types_supported(const accb_gemm_desc& d);   // element types only, whatever the layout
 // want_two_sm: 1 = CTA pairs (cta_group::2), 0 = single CTAs, -1 = whichever tile shape suits the problem.
 int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err);
 // host only: the tile shape launch_gemm_umma would pick (from d, batch, num_sms, max_ctas) and the rounds of tiles it gives
@@ -88,6 +90,10 @@ void gemm_umma_tile_plan(const GemmLaunch& g, int want_two_sm, int* two_sm, int*
 // host only: grid, block and dynamic shared memory of the launch launch_gemm_umma would make (out[0..2] grid,
 // out[3..5] block, out[6] dynamic shared-memory bytes, out[7] pipeline stages)
 void gemm_umma_launch_geometry(const GemmLaunch& g, int want_two_sm, int32_t out[8]);
+
+// gemm_splitk.cu: C <- epi(alpha * sum of `slices` dense row-major M x N partials (fp32, or int32 for an int32 C) + beta * C + bias)
+int launch_splitk_reduce(const void* partial, int slices, const accb_gemm_desc& d, void* c, const float* bias,
+                         cudaStream_t stream, const char** err);
 
 // reduce_mean.cu
 // Scratch (fp32 partial sums) a launch needs for these dims, in bytes; 0 when the

@@ -1314,7 +1314,7 @@ TileChoice choose_tile(const GemmLaunch& g, int want_two_sm /* -1: free, 0 / 1: 
     // 1518 / 1346 / 972 / 851 TFLOP/s at 8192^3).  128-column tiles need 1.5x the L2 -> shared-memory traffic
     // per flop and are bound by it; they only pay on problems too small to give every SM a 256-column tile.
     static const double kEff[2][2] = { /* 1 SM */ { 0.64 /*128*/, 0.89 /*256*/ }, /* pair */ { 0.56 /*128*/, 1.00 /*256*/ } };
-    const int force_bn = options().gemm_tile_cols;
+    const int force_bn = g.force_tile_cols ? g.force_tile_cols : options().gemm_tile_cols;
     TileChoice best{want_two_sm != 0, kBlockN};
     double best_cost = -1.0;
     for (int two = 1; two >= 0; --two) {
@@ -1379,15 +1379,23 @@ void gemm_umma_launch_geometry(const GemmLaunch& g, int want_two_sm, int32_t out
     out[7] = stages;
 }
 
-bool gemm_umma_supported(const GemmLaunch& g, const char** why)
+bool gemm_umma_types_supported(const accb_gemm_desc& d)
 {
-    const accb_gemm_desc& d = g.d;
     const int a = d.a_type, b = d.b_type, c = d.c_type;
     const bool f16_family = (a == ACCB_F16 && b == ACCB_F16 && (c == ACCB_F32 || c == ACCB_F16)) ||
                             (a == ACCB_BF16 && b == ACCB_BF16 && (c == ACCB_F32 || c == ACCB_BF16));
     const bool tf32 = (a == ACCB_F32 && b == ACCB_F32 && c == ACCB_F32);
     const bool i8 = ((a == ACCB_S8 || a == ACCB_U8) && (b == ACCB_S8 || b == ACCB_U8) && c == ACCB_S32);
-    if (!(f16_family || tf32 || i8)) { *why = "element types have no tensor-core path"; return false; }
+    return f16_family || tf32 || i8;
+}
+
+bool gemm_umma_supported(const GemmLaunch& g, const char** why)
+{
+    const accb_gemm_desc& d = g.d;
+    const int a = d.a_type, b = d.b_type, c = d.c_type;
+    const bool tf32 = (a == ACCB_F32 && b == ACCB_F32 && c == ACCB_F32);
+    const bool i8 = ((a == ACCB_S8 || a == ACCB_U8) && (b == ACCB_S8 || b == ACCB_U8) && c == ACCB_S32);
+    if (!gemm_umma_types_supported(d)) { *why = "element types have no tensor-core path"; return false; }
     if (i8 && (d.alpha != 1.0f || (d.beta != 0.0f && d.beta != 1.0f) || g.bias)) { *why = "integer GEMM supports alpha=1, beta in {0,1}, no bias"; return false; }
     // each operand must be contiguous along K (row-major A / column-major B) or along M / N (column-major A /
     // row-major B); the other stride is the pitch

@@ -434,3 +434,93 @@ def test_reference_int16_matmul_recipe(tmp_path, m, n, k):
     assert np.array_equal(c, oracle.gemm(a, b.T, np.zeros((m, n), np.int32)))
     fns[fn.name](a, b, c)                            # C is INPUT_OUTPUT: a second call accumulates
     assert np.array_equal(c, 2 * c_ref)
+
+
+@pytest.mark.parametrize("kind,out_kind,m,n,k,a_order,b_order", [
+    ("bfloat16", "bfloat16", 768, 320, 3053, "C", "C"),      # odd K, row-major A: rows of 6106 bytes
+    ("float16", "float32", 300, 264, 1001, "C", "F"),        # both operands K-contiguous with an odd K
+    ("int8", "int32", 520, 128, 1999, "C", "F"),
+    ("bfloat16", "float32", 1001, 512, 256, "F", "C"),       # column-major A with an odd M, row-major B
+])
+def test_operands_with_unaligned_rows_are_repacked_for_the_tensor_cores(kind, out_kind, m, n, k, a_order, b_order):
+    # "tensor_preferred" (what a tensorized plan asks for) must give the tensor-core result for operands whose rows are
+    # not a multiple of 16 bytes - the reference's BERT list has K = 30522 - and must not fall back to the slow kernel
+    before = rt.launch_count()
+    _tensor_case_preferred(kind, out_kind, m, n, k, a_order, b_order)
+    # one pitched copy per repacked operand + the GEMM: more launches than the single CUDA-core kernel would count
+    assert rt.launch_count() - before >= 2
+    with pytest.raises(rt.AccbError):                       # an explicit tensor request still refuses the layout
+        _tensor_case_preferred(kind, out_kind, m, n, k, a_order, b_order, compute="tensor")
+
+
+def _tensor_case_preferred(kind, out_kind, m, n, k, a_order, b_order, compute="tensor_preferred"):
+    rng = np.random.default_rng(m + n + k)
+    lay = lambda x, o: np.asfortranarray(x) if o == "F" else np.ascontiguousarray(x)
+    if kind == "int8":
+        A = lay(rng.integers(-128, 128, size=(m, k)).astype(np.int8), a_order)
+        B = lay(rng.integers(-128, 128, size=(k, n)).astype(np.int8), b_order)
+        C0 = rng.integers(-1000, 1000, size=(m, n)).astype(np.int32)
+        want = oracle.gemm(A, B, C0.copy(), relu=True)
+        got = C0.copy()
+        rt.gemm(A, B, got, relu=True, compute=compute)
+        assert np.array_equal(got, want)
+        return
+    Af = rng.standard_normal((m, k), dtype=np.float32)
+    Bf = rng.standard_normal((k, n), dtype=np.float32) / np.float32(np.sqrt(k))
+    kw = {}
+    if kind == "float16":
+        A, B = lay(Af.astype(np.float16), a_order), lay(Bf.astype(np.float16), b_order)
+        A64, B64 = A.astype(np.float64), B.astype(np.float64)
+    else:
+        A, B = lay(oracle.f32_to_bf16_bits(Af), a_order), lay(oracle.f32_to_bf16_bits(Bf), b_order)
+        A64, B64 = oracle.bf16_bits_to_f32(A).astype(np.float64), oracle.bf16_bits_to_f32(B).astype(np.float64)
+        kw["kind"] = "bfloat16"
+    C0f = rng.standard_normal((m, n), dtype=np.float32)
+    if out_kind == "bfloat16":
+        C0 = oracle.f32_to_bf16_bits(C0f)
+        kw["out_kind"] = "bfloat16"
+    else:
+        C0 = C0f
+    want = oracle.gemm(A, B, C0.copy(), in_kind=kind, out_kind=out_kind, relu=True)
+    got = C0.copy()
+    rt.gemm(A, B, got, relu=True, compute=compute, **kw)
+    gf = oracle.bf16_bits_to_f32(got) if out_kind == "bfloat16" else got
+    wf = oracle.bf16_bits_to_f32(want) if out_kind == "bfloat16" else want
+    scale = np.abs(A64) @ np.abs(B64) + np.abs(C0f)
+    assert (np.abs(gf.astype(np.float64) - wf) <= 2e-2 * np.maximum(np.abs(wf), scale)).all()
+    tight = 1e-2 if out_kind == "bfloat16" else 1e-4
+    assert (np.abs(gf.astype(np.float64) - wf) <= tight * np.maximum(np.abs(wf), scale)).all()
+
+
+@pytest.mark.parametrize("kind,out_kind,m,n,k,a_order,b_order", [
+    ("bfloat16", "bfloat16", 256, 512, 16384, "C", "F"),     # 2 tiles, K cut into 16 slices
+    ("float16", "float32", 512, 1024, 16384, "F", "C"),      # 8 wide tiles, 8 slices, column-major A / row-major B
+    ("int8", "int32", 256, 256, 16384, "C", "F"),            # exact
+    ("bfloat16", "float32", 200, 300, 12800, "C", "C"),      # ragged M and N
+    ("bfloat16", "bfloat16", 768, 320, 30522, "C", "C"),     # the BERT vocabulary shape: repacked, K padded to 30720, 12 slices
+])
+def test_few_tiles_and_a_long_k_are_split_along_k(kind, out_kind, m, n, k, a_order, b_order):
+    before = rt.launch_count()
+    _tensor_case_preferred(kind, out_kind, m, n, k, a_order, b_order)
+    assert rt.launch_count() - before >= 2                  # the batched launch over the slices and the reduction pass
+    # the split is deterministic: the same bits on every run
+    import torch
+    dev = torch.device("cuda:0")
+    if kind != "int8":
+        dt = torch.bfloat16 if kind == "bfloat16" else torch.float16
+        A = torch.randn(m, k, device=dev).to(dt)
+        B = (torch.randn(n, k, device=dev) / k ** 0.5).to(dt).t()
+        outs = []
+        for _ in range(2):
+            C = torch.zeros(m, n, device=dev)
+            rt.gemm(A, B, C, beta=0.0, compute="tensor_preferred")
+            rt.synchronize()
+            outs.append(C)
+        assert torch.equal(outs[0], outs[1])
+        if (k * 2) % 16:
+            return                                          # the explicit tensor modes refuse rows that are not 16-byte aligned
+        # and close to the unsplit launch of the same problem
+        C1 = torch.zeros(m, n, device=dev)
+        rt.gemm(A, B, C1, beta=0.0, compute="tensor_2sm" if m > 128 else "tensor")
+        rt.synchronize()
+        assert (outs[0] - C1).abs().max().item() <= 1e-4 * (A.float().abs() @ B.float().abs()).max().item()
