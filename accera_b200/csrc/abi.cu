@@ -624,7 +624,7 @@ int accb_set_option(const char* name, int64_t value)
     const int v = (int)value;
     if (n == "reset") { o = Options(); return ACCB_OK; }
     if (n == "gemm.tile_cols") { if (v != 0 && v != 128 && v != 256) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.tile_cols is 0, 128 or 256"); o.gemm_tile_cols = v; }
-    else if (n == "gemm.staged_store") o.gemm_staged_store = v < 0 ? -1 : (v ? 1 : 0);
+    else if (n == "gemm.staged_store") o.gemm_staged_store = v < 0 ? -1 : (v > 2 ? 1 : (int)v);
     else if (n == "gemm.pace_pct") { if (v > 100) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.pace_pct is -1 or 0..100"); o.gemm_pace_pct = v < 0 ? -1 : v; }
     else if (n == "gemm.group_m") { if (v < 0 || v > 4096) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.group_m is 0..4096"); o.gemm_group_m = v; }
     else if (n == "gemm.hint_a") o.gemm_hint_a = (v >= 0 && v <= 2) ? v : 0;
@@ -635,6 +635,7 @@ int accb_set_option(const char* name, int64_t value)
     else if (n == "gemm.wait_limit_us") { if (value < 0 || value > 10000000) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.wait_limit_us is 0 (default) .. 10000000"); o.gemm_wait_limit_us = v; }
     else if (n == "gemm.test_drop_commit") o.gemm_test_drop_commit = v ? 1 : 0;
     else if (n == "gemm.pdl") o.gemm_pdl = v < 0 ? -1 : (v ? 1 : 0);
+    else if (n == "gemm.c_in") o.gemm_c_in = v < 0 ? -1 : (v ? 1 : 0);
     else if (n == "gemm.verbose") o.gemm_verbose = v ? 1 : 0;
     else if (n == "host_gemm.stage_chunks") { if (v < 0 || v > 256) return fail(ACCB_ERR_ARG, "accb_set_option: host_gemm.stage_chunks is 0 (default) .. 256"); o.host_stage_chunks = v; }
     else if (n == "reduce.rows_threads_per_output") { if (v != 0 && v != 32 && v != 64 && v != 128 && v != 256) return fail(ACCB_ERR_ARG, "accb_set_option: reduce.rows_threads_per_output is 0, 32, 64, 128 or 256"); o.reduce_rows_tpr = v; }

@@ -74,6 +74,10 @@ template <bool TWO_SM, int BN> struct SmemPlan {
     // as many stages as fit beside the staging boxes: 4 (1 SM, 256), 6 (pair, 256 / 1 SM, 128), 8 (pair, 128)
     static constexpr int kBudget = 227 * 1024 - 1024 - kBarrierBytes - kStoreBytes;   // 227 KB per CTA on sm_100
     static constexpr int kStages = kBudget / kStageBytes > 8 ? 8 : kBudget / kStageBytes;
+    // launches that also bring the old C in through the staging boxes (c_in) use four boxes per epilogue warp; the
+    // second kStoreBytes are taken from the end of the operand ring: 5, 6, 3 and 5 stages remain
+    static constexpr int kCinBoxes = 4;
+    static constexpr int kCinStages = kStages - (kStoreBytes + kStageBytes - 1) / kStageBytes;
     static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + kStoreBytes + 1024;   // +1024: manual alignment
     static constexpr int kTmemCols = 2 * BN;   // two accumulators of BN fp32 columns (a power of two >= 32)
 };
@@ -118,6 +122,11 @@ struct UmmaParams {
                             // of the local C to the replicas (see copy_tiles).  The computing CTAs then store to C only.
     int* tile_flags;        // copy_ctas > 0: one counter per tile, bumped by every epilogue warp once its part of the
                             // tile is in C; zeroed by the host before the launch
+    int lsu_stage;          // staged epilogue whose boxes are moved between shared and global memory by the warp itself
+                            // (coalesced 16-byte accesses) instead of by TMA; taken for short K loops, where a TMA store or
+                            // load of C queues behind the operand loads of several pipeline stages
+    int c_in;               // lsu_stage with beta != 0: the old C is copied into the staging boxes boxes ahead (cp.async,
+                            // also across tiles) instead of being read row by row when it is needed
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -328,6 +337,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
+        : "memory");
+}
+
+// Waits for this thread's outstanding tcgen05.ld.  The registers of the load are passed through the statement so
+// that the compiler orders every use of them after the wait (a load may be issued well before its data is needed).
+__device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.wait::ld.sync.aligned;"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+          "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        :
         : "memory");
 }
 
@@ -585,6 +608,84 @@ __device__ __forceinline__ void epilogue_to_smem(const uint32_t (&acc)[32], cons
     }
 }
 
+// The staged epilogue when the old C is already in the staging box (brought there by a TMA load): this thread's
+// 32 results are combined with the C values found in their own 16-byte slots and written back over them.  Rows and
+// columns outside the matrix were zero-filled by the load and are clipped by the store.
+template <typename TC, typename ACC>
+__device__ __forceinline__ void epilogue_inplace(const uint32_t (&acc)[32], int64_t col0, int ncols,
+                                                 const float* __restrict__ bias, const UmmaParams& p, uint8_t* srow,
+                                                 int slot0, int lane7)
+{
+    if constexpr (std::is_same<ACC, int>::value) {
+        int v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (int)acc[j];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int4 o = *reinterpret_cast<const int4*>(srow + (((slot0 + q) ^ lane7) << 4));
+            v[4 * q] += o.x; v[4 * q + 1] += o.y; v[4 * q + 2] += o.z; v[4 * q + 3] += o.w;
+        }
+        if (p.relu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = max(v[j], 0);
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<int4*>(srow + (((slot0 + q) ^ lane7) << 4)) = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    } else {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
+        if (p.alpha != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+        }
+        if constexpr (sizeof(TC) == 4) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 o = *reinterpret_cast<const float4*>(srow + (((slot0 + q) ^ lane7) << 4));
+                v[4 * q] += p.beta * o.x; v[4 * q + 1] += p.beta * o.y;
+                v[4 * q + 2] += p.beta * o.z; v[4 * q + 3] += p.beta * o.w;
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4 o = *reinterpret_cast<const uint4*>(srow + (((slot0 + q) ^ lane7) << 4));
+                const TC* h = reinterpret_cast<const TC*>(&o);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[8 * q + e] += p.beta * (float)h[e];
+            }
+        }
+        if (bias) {
+            if (ncols == 32) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += __ldg(bias + col0 + j);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += __ldg(bias + col0 + j);
+            }
+        }
+        if (p.relu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+        }
+        if constexpr (sizeof(TC) == 4) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(srow + (((slot0 + q) ^ lane7) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                TC* h = reinterpret_cast<TC*>(&o);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) h[e] = (TC)v[8 * q + e];
+                *reinterpret_cast<uint4*>(srow + (((slot0 + q) ^ lane7) << 4)) = o;
+            }
+        }
+    }
+}
+
 template <int KIND> struct ElemBytes { static constexpr int value = (KIND == KIND_F16) ? 2 : (KIND == KIND_TF32) ? 4 : 1; };
 
 // One TMA box of an operand.  BATCHED launches address a batched operand through its rank-3 map (the problem is
@@ -801,19 +902,21 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     using Plan = SmemPlan<TWO_SM, BN>;
     using ACC = typename std::conditional<KIND == KIND_I8, int, float>::type;
     constexpr int kTmemCols = Plan::kTmemCols;
-    constexpr int S = Plan::kStages;
+    constexpr int SMAX = Plan::kStages;
+    // stages in use: launches that load C through the staging boxes give the end of the ring to two more boxes per warp
+    const int S = p.c_in ? Plan::kCinStages : SMAX;
     constexpr int kCtas = TWO_SM ? 2 : 1;
 
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128B swizzle pattern shared by TMA and the MMA descriptors
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t bars = smem_base + S * Plan::kStageBytes + Plan::kStoreBytes;
+    const uint32_t bars = smem_base + SMAX * Plan::kStageBytes + Plan::kStoreBytes;
     auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
-    auto tmem_full_bar = [&](int b) { return bars + 8u * (2 * S + b); };
-    auto tmem_empty_bar = [&](int b) { return bars + 8u * (2 * S + 2 + b); };
-    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_gen + S * Plan::kStageBytes + Plan::kStoreBytes + 8 * (2 * S + 4));
+    auto empty_bar = [&](int s) { return bars + 8u * (SMAX + s); };
+    auto tmem_full_bar = [&](int b) { return bars + 8u * (2 * SMAX + b); };
+    auto tmem_empty_bar = [&](int b) { return bars + 8u * (2 * SMAX + 2 + b); };
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_gen + SMAX * Plan::kStageBytes + Plan::kStoreBytes + 8 * (2 * SMAX + 4));
     // gave_up[r] != 0: a bounded wait of the CTA with rank r in the pair ran out.  Each CTA keeps a copy of both
     // words (a CTA that gives up also writes its word into its partner's copy), so that after the closing barrier
     // both CTAs of a pair take the same teardown path without touching global memory.
@@ -852,7 +955,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         gave_up[1] = 0u;
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
-        for (int s = 0; s < S; ++s) {
+        for (int s = 0; s < SMAX; ++s) {
             mbar_init(full_bar(s), 1);    // the producer's arrive.expect_tx (pair: rank 0's, covering both CTAs' bytes)
             mbar_init(empty_bar(s), 1);   // one tcgen05.commit
         }
@@ -1002,7 +1105,48 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int local = 0;
         bool ok = true;
         uint32_t store_count = 0;                    // TMA-store boxes this warp has issued (warp-uniform)
-        uint8_t* store_stage = smem_gen + S * Plan::kStageBytes + (size_t)(warp - 2) * 2 * Plan::kStoreBoxBytes;
+        const uint32_t n_boxes = p.c_in ? (uint32_t)Plan::kCinBoxes : 2u;     // staging boxes of this warp
+        uint8_t* store_stage = smem_gen + S * Plan::kStageBytes + (size_t)(warp - 2) * n_boxes * Plan::kStoreBoxBytes;
+        // c_in: the old C of every box this warp will produce is copied (cp.async, 16 bytes per lane, 8 lanes per
+        // 128-byte row, swizzled like the box) into the staging box the result is later written to, in the order in
+        // which the boxes are produced and as far ahead as the ring allows - the first boxes of the next tile while
+        // this warp still waits for that tile's accumulator.  The n-th copy and the n-th result use box n % n_boxes.
+        constexpr int kBoxCols = 128 / (int)sizeof(TC);          // columns per staging box
+        constexpr int kBoxesPerTile = BN / kBoxCols;
+        constexpr int kPerVec = 16 / (int)sizeof(TC);
+        const int vu = lane & 7, vr4 = lane >> 3;                // this lane's 16-byte unit and row (mod 4) in box moves
+        uint32_t cin_issued = 0;                     // boxes whose copy has been issued (warp-uniform)
+        int cin_t = unit, cin_box = 0;               // the tile and the box in it that is copied next
+        int64_t cin_row0 = 0, cin_col_tile = 0;
+        auto cin_issue_upto = [&](uint32_t limit) {
+            while (cin_issued < limit && cin_t < num_tiles) {
+                if (cin_box == 0) {
+                    int problem, tm, tn;
+                    tile_coords_batched(cin_t, p, problem, tm, tn);
+                    cin_row0 = (int64_t)(tm * kCtas + (int)rank) * kBlockM + q * 32;
+                    cin_col_tile = (int64_t)tn * BN;
+                }
+                const int64_t box_col0 = cin_col_tile + (int64_t)cin_box * kBoxCols;
+                if (cin_row0 < p.m && box_col0 < p.n) {
+                    uint8_t* dst_box = store_stage + (size_t)(cin_issued % n_boxes) * Plan::kStoreBoxBytes;
+                    const int64_t col = box_col0 + (int64_t)vu * kPerVec;
+                    const bool col_ok = col + kPerVec <= p.n;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = 4 * i + vr4;
+                        uint8_t* dst = dst_box + r * 128 + ((vu ^ (r & 7)) << 4);
+                        if (col_ok && cin_row0 + r < p.m)
+                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(C + (cin_row0 + r) * p.cs0 + col) : "memory");
+                        else
+                            *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);    // outside the matrix: never stored
+                    }
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    ++cin_issued;
+                }
+                if (++cin_box == kBoxesPerTile) { cin_box = 0; cin_t += num_units; }
+            }
+        };
+        if (p.c_in) cin_issue_upto(n_boxes);
         for (int t = unit; t < num_tiles && ok; t += num_units, ++local) {
             int problem, tm, tn;
             tile_coords_batched(t, p, problem, tm, tn);
@@ -1016,13 +1160,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             TC* crow = C + (int64_t)problem * p.c_bs + row * p.cs0;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
             const int64_t row0 = (int64_t)(tm * kCtas + (int)rank) * kBlockM + q * 32;     // first row of this warp
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t acc[32];
-                tmem_ld32(taddr + (uint32_t)(c * 32), acc);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            auto process_chunk = [&](int c, const uint32_t (&acc)[32]) {
                 const int64_t col0 = col_tile + c * 32;
-                if (!p.tma_store) {
+                if (!p.tma_store && !p.lsu_stage) {
                     if (row < p.m && col0 < p.n) {
                         const int ncols = (int)min((int64_t)32, p.n - col0);
                         epilogue_row<TC, ACC>(acc, crow, col0, ncols, c_vec, p.cs1, bias, p);
@@ -1033,18 +1173,54 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const int sub = c % CPB;
                     const int64_t box_col0 = col0 - (int64_t)sub * 32;
                     const bool box_live = (row0 < p.m) && (box_col0 < p.n);      // warp-uniform
-                    uint8_t* box = store_stage + (size_t)(store_count & 1u) * Plan::kStoreBoxBytes;
-                    if (box_live && sub == 0 && store_count >= 2) {
-                        // the box about to be overwritten was handed to TMA two boxes ago: wait until it has been read
-                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    uint8_t* box = store_stage + (size_t)(store_count % n_boxes) * Plan::kStoreBoxBytes;
+                    if (p.c_in) {
+                        if (box_live && sub == 0) {
+                            // the old C of this box was requested boxes ago: wait for this lane's part of it, leaving the
+                            // copies of the boxes after it in flight, then for the other lanes' parts
+                            switch (cin_issued - 1u - store_count) {
+                            case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+                            case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+                            case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+                            default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+                            }
+                            __syncwarp();
+                        }
+                        if (box_live && col0 < p.n) {
+                            const int ncols = (int)min((int64_t)32, p.n - col0);
+                            epilogue_inplace<TC, ACC>(acc, col0, ncols, bias, p, box + lane * 128, sub * (32 * (int)sizeof(TC) / 16), lane & 7);
+                        }
+                    } else {
+                        if (box_live && sub == 0 && store_count >= 2 && !p.lsu_stage) {
+                            // the box about to be overwritten was handed to TMA two boxes ago: wait until it has been read
+                            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                            __syncwarp();
+                        }
+                        if (box_live && col0 < p.n) {
+                            const int ncols = (int)min((int64_t)32, p.n - col0);
+                            epilogue_to_smem<TC, ACC>(acc, crow, row < p.m, col0, ncols, c_vec, bias, p, box + lane * 128,
+                                                      sub * (32 * (int)sizeof(TC) / 16), lane & 7);
+                        }
+                    }
+                    if (box_live && sub == CPB - 1 && p.lsu_stage) {
+                        // the warp moves the finished box to C itself: 8 lanes per 128-byte row, 4 rows per step
                         __syncwarp();
-                    }
-                    if (box_live && col0 < p.n) {
-                        const int ncols = (int)min((int64_t)32, p.n - col0);
-                        epilogue_to_smem<TC, ACC>(acc, crow, row < p.m, col0, ncols, c_vec, bias, p, box + lane * 128,
-                                                  sub * (32 * (int)sizeof(TC) / 16), lane & 7);
-                    }
-                    if (box_live && sub == CPB - 1) {
+                        const int64_t col = box_col0 + (int64_t)vu * kPerVec;
+                        const bool col_ok = col + kPerVec <= p.n;
+                        uint4 v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = 4 * i + vr4;
+                            v[i] = *reinterpret_cast<const uint4*>(box + r * 128 + ((vu ^ (r & 7)) << 4));
+                        }
+                        TC* dst = C + (row0 + vr4) * p.cs0 + col;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (col_ok && row0 + 4 * i + vr4 < p.m) *reinterpret_cast<uint4*>(dst + (int64_t)(4 * i) * p.cs0) = v[i];
+                        __syncwarp();                // the box may be written again
+                        ++store_count;
+                        if (p.c_in) cin_issue_upto(store_count + n_boxes);
+                    } else if (box_live && sub == CPB - 1) {
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to TMA
                         __syncwarp();
                         if (lane == 0) {
@@ -1080,11 +1256,29 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         ++store_count;
                     }
                 }
+            };
+            // The accumulator is read 32 columns at a time, the next chunk's tcgen05.ld in flight while this one is
+            // worked on (two register sets).
+            {
+                uint32_t acc0[32], acc1[32];
+                tmem_ld32(taddr, acc0);
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; c += 2) {
+                    tmem_wait_ld(acc0);
+                    tmem_ld32(taddr + (uint32_t)((c + 1) * 32), acc1);
+                    process_chunk(c, acc0);
+                    tmem_wait_ld(acc1);
+                    if (c + 2 < BN / 32) {
+                        tmem_ld32(taddr + (uint32_t)((c + 2) * 32), acc0);
+                    } else {
+                        // the whole accumulator is in registers: hand it back to the MMA issuer before the last chunk's work
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(TWO_SM ? (tmem_empty_bar(buf) & kPeerMask) : tmem_empty_bar(buf));
+                    }
+                    process_chunk(c + 1, acc1);
+                }
             }
-            // this warp has drained its part of the accumulator: hand it back to the MMA issuer
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(TWO_SM ? (tmem_empty_bar(buf) & kPeerMask) : tmem_empty_bar(buf));
             if (p.copy_ctas > 0 && lane == 0) {
                 // this warp's part of the tile is on its way to C: once the stores have completed, publish it to
                 // the forwarding CTAs (TMA writes belong to the async proxy, the readers use ordinary loads)
@@ -1289,6 +1483,7 @@ int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap
         fprintf(stderr, "tcgen05 GEMM %lld x %lld x %lld x %d: %s tiles of %d columns, %d tiles on %d %s, pacing %d%%\n",
                 (long long)p.m, (long long)p.n, (long long)p.k, p.batch, TWO_SM ? "pair" : "single-CTA", BN, num_tiles, units,
                 TWO_SM ? "pairs" : "CTAs", p.pace_pct);
+    if (p.verbose && p.lsu_stage) fprintf(stderr, "  staged epilogue without TMA%s, %d operand stages\n", p.c_in ? ", old C copied in boxes ahead" : "", p.c_in ? Plan::kCinStages : Plan::kStages);
     if (p.verbose && p.n_replicas > 1)
         fprintf(stderr, "  %d replicas: %s\n", p.n_replicas, p.copy_ctas > 0 ? "forwarding CTAs" : p.peer_store ? "register stores from the epilogue" : "TMA stores from the epilogue");
     cfg.gridDim = dim3((unsigned)((units + copy_units) * (TWO_SM ? 2 : 1)));
@@ -1442,6 +1637,7 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
 
     const bool int_acc = (d.c_type == ACCB_S32);
     UmmaParams p;
+    memset(&p, 0, sizeof p);
     p.m = d.m; p.n = d.n; p.k = d.k;
     p.cs0 = d.c_stride[0]; p.cs1 = d.c_stride[1];
     p.alpha = d.alpha; p.beta = d.beta; p.relu = (d.epilogue == ACCB_EPI_RELU);
@@ -1485,6 +1681,21 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
         p.peer_store = (g.n_extra_c > 0 && vec_rows && (o.gemm_peer_store < 0 ? kPeerStoreDefault : o.gemm_peer_store)) ? 1 : 0;
     }
     p.launch_id = g.launch_id;
+    // beta != 0 and a short K loop (up to 32 slabs of 128 bytes: K = 2048 for 16-bit operands): the epilogue of a
+    // CTA's last tile is a large part of the launch, and most of it is waiting for the old C, read row by row when it
+    // is needed.  There the epilogue warps copy the old C into their staging boxes boxes ahead (the first boxes of a
+    // tile while its K loop still runs) and move the boxes to C themselves; the extra boxes cost the operand ring one
+    // stage (two for narrow pair tiles).  Measured, C += A @ B in bf16, against the TMA-staged epilogue: 1024^3 10.0
+    // against 11.5 us, 2048^3 19.7 / 22.2, 3072 x 2048 x 1024 21.1 / 24.9; equal at K = 4096 (4096^3 116 / 116), 2 %
+    // slower at 65536 x 8192 x 8192 (6.70 / 6.56 ms), which is why long K loops keep the TMA stores.
+    {
+        const int64_t slabs = (d.k * elem_size(d.a_type) + kSlabBytes - 1) / kSlabBytes;
+        const Options& o = options();
+        const bool can = p.tma_store && g.n_extra_c == 0 && ((d.n * elem_size(d.c_type)) % 16) == 0;
+        const bool short_k = slabs <= 32;
+        if (can && (o.gemm_staged_store == 2 || (o.gemm_staged_store < 0 && short_k && d.beta != 0.0f))) { p.lsu_stage = 1; p.tma_store = 0; }
+        p.c_in = (p.lsu_stage && d.beta != 0.0f && (o.gemm_c_in >= 0 ? o.gemm_c_in : 1)) ? 1 : 0;
+    }
     for (int r = 0; r < kMaxReplicas - 1; ++r) p.peer_c[r] = r < g.n_extra_c ? g.extra_c[r] : nullptr;
     // Forwarding CTAs: with three or more replicas to feed, the bytes leaving for other GPUs are a large share of
     // the launch and are better sent from SMs of their own (see copy_tiles).  With one or two the epilogue's own

@@ -1,6 +1,6 @@
 """Runs one hot-path kernel a few times on device-resident inputs - the command to put under a profiler.
 
-    python -m accera_b200.profile_cases gemm_bf16 [--m 8192 --n 8192 --k 8192] [--compute tensor_2sm] [--iters 3]
+    python -m accera_b200.profile_cases gemm_bf16 [--m 8192 --n 8192 --k 8192] [--compute tensor_2sm] [--iters 3] [--beta 1.0]
     python -m accera_b200.profile_cases reduce_mean [--rows 8192 --cols 4096]
     python -m accera_b200.profile_cases gather [--table-rows 32000 --cols 4096 --indices 16384]
     python -m accera_b200.profile_cases matmul_relu_f32 [--m 512 --n 512 --k 512]
@@ -35,6 +35,7 @@ def main() -> None:
     ap.add_argument("--indices", type=int, default=16384)
     ap.add_argument("--compute", default="tensor_2sm")
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--beta", type=float, default=1.0, help="GEMM cases: C <- A @ B + beta * C")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="a launch override for this run, e.g. gemm.group_n=16 (see accb_set_option)")
     a = ap.parse_args()
@@ -59,7 +60,7 @@ def main() -> None:
             B = (torch.randn(n, k, device=dev) / k ** 0.5).to(dt).t()
             C = torch.zeros(m, n, device=dev, dtype=dt if a.case == "gemm_bf16" else torch.float32)
         for _ in range(a.iters):
-            rt.gemm(A, B, C, beta=1.0, relu=a.case != "gemm_s8", compute=a.compute)
+            rt.gemm(A, B, C, beta=a.beta, relu=a.case != "gemm_s8", compute=a.compute)
     elif a.case == "matmul_relu_f32":
         m, n, k = a.m or 512, a.n or 512, a.k or 512
         A = torch.rand(m, k, device=dev); B = torch.rand(k, n, device=dev); C = torch.zeros(m, n, device=dev)

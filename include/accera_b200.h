@@ -92,7 +92,11 @@ typedef struct accb_gemm_desc {
                                        make progress while the GEMM computes. */
 } accb_gemm_desc;
 
-/* bias may be NULL; when given it is n fp32 values added to every row before the ReLU */
+/* bias may be NULL; when given it is n fp32 values added to every row before the ReLU.
+ * Memory: host-pointer calls stage through a cached per-device workspace.  A device-pointer call allocates only in two
+ * cases, both from the stream-ordered allocator on the launch stream (freed on it right after the launch): 16-bit or
+ * 8-bit operands whose rows are not 16-byte aligned are repacked into aligned rows for the tensor cores, and few-tile
+ * long-K problems that are split along K keep their fp32 partial sums there. */
 int accb_gemm(const accb_gemm_desc* desc, const void* a, const void* b, void* c, const float* bias);
 
 /*
@@ -139,8 +143,14 @@ int accb_gemm_launch_geometry(const accb_gemm_desc* desc, int64_t batch, int32_t
  * (No counterpart in the reference, which has no multi-GPU path.)  c_replicas[0] is the local C: it is
  * read when beta != 0 and written; c_replicas[1..n_replicas-1] receive the same values with the same
  * layout and are only written.  They may be another GPU's memory mapped into this process (peer /
- * symmetric memory): every output tile is then pushed over NVLink by TMA stores straight from the
- * epilogue, so an M-row sharded GEMM reassembles C on all GPUs without a separate all-gather.
+ * symmetric memory): every output tile is then pushed over NVLink from inside the GEMM kernel, so an
+ * M-row sharded GEMM reassembles C on all GPUs without a separate all-gather.  With 1 or 2 extra
+ * replicas the computing CTAs' epilogues TMA-store each staged box to every replica; with 3 or more,
+ * a few CTAs of the same launch (18, or 32 from 6 extra replicas on) do no math and forward finished
+ * tiles instead: they wait for a tile's completion counter, TMA-load the tile from the local C (L2)
+ * into a shared-memory ring and write it to every other replica with 16-byte stores - stores that
+ * wait for NVLink credit then never stall an SM that feeds the tensor cores.  Peer memory is only
+ * ever stored to, never loaded from.  "gemm.copy_ctas" overrides the number of forwarding CTAs.
  * Device pointers only; C must be row-major with a 16-byte aligned pitch and base; 1 <= n_replicas <= 8.
  * The kernel's stores have completed when the launch has completed on its stream; making them visible
  * to the other GPUs' later work (a barrier between the ranks) is the caller's job.
@@ -262,7 +272,8 @@ const char* accb_version(void);
  * code path on small problems, for tuning runs, and for the self-test of the time-out path; none is needed in
  * normal use and none has a counterpart in the reference.  accb_set_option("reset", 0) restores all defaults.
  *   "gemm.tile_cols"         0 (choose) | 128 | 256   accumulator columns per tile of the tensor-core GEMM
- *   "gemm.staged_store"      -1 (choose) | 0 | 1      epilogue through shared memory + TMA stores (1) or from registers (0)
+ *   "gemm.staged_store"      -1 (choose) | 0 | 1 | 2  epilogue from registers (0), through shared-memory boxes stored by TMA (1),
+ *                                                     or through boxes that the epilogue warps move themselves (2)
  *   "gemm.pace_pct"          -1 (choose) | 0..100     tile-by-tile pacing of the persistent CTAs
  *   "gemm.group_m"           0 (choose) | rows        tile rows visited together
  *   "gemm.hint_a" / "gemm.hint_b"   0 | 1 | 2         L2 eviction priority of the operand loads
@@ -276,6 +287,8 @@ const char* accb_version(void);
  *                                                     ACCB_ERR_TIMEOUT (no fault, no trap; the context stays usable)
  *   "gemm.pdl"               -1 (on) | 0 | 1          programmatic dependent launch: the next GEMM of a stream is scheduled
  *                                                     and sets itself up while the previous kernel still runs
+ *   "gemm.c_in"              -1 (choose) | 0 | 1      beta != 0 with warp-moved boxes: the old C is copied into the boxes ahead
+ *                                                     of its use (1) or read row by row when needed (0)
  *   "gemm.verbose"           0 | 1                    print the launch plan to stderr
  *   "host_gemm.stage_chunks" 0 (16) | 1..256          row chunks of the staged host-pointer GEMM
  *   "reduce.rows_threads_per_output"  0 (choose) | 32 | 64 | 128 | 256   reduce_mean over contiguous segments

@@ -524,3 +524,59 @@ def test_few_tiles_and_a_long_k_are_split_along_k(kind, out_kind, m, n, k, a_ord
         rt.gemm(A, B, C1, beta=0.0, compute="tensor_2sm" if m > 128 else "tensor")
         rt.synchronize()
         assert (outs[0] - C1).abs().max().item() <= 1e-4 * (A.float().abs() @ B.float().abs()).max().item()
+
+
+# ---------------------------------------------------------------------------
+# the three ways the tensor-core epilogue brings C in and out give the same bits
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("compute", ["tensor", "tensor_2sm"])
+@pytest.mark.parametrize("kind,out_kind,m,n,k", [
+    ("bfloat16", "bfloat16", 1024, 1024, 1024),     # one tile per CTA: the old C of the first boxes is copied during the K loop
+    ("bfloat16", "bfloat16", 2500, 1000, 320),      # several tiles per CTA on the narrow grid below, ragged M and N
+    ("float16", "float32", 700, 520, 256),          # 4-byte results: one chunk per box
+    ("float16", "float16", 130, 72, 64),            # a single partial tile
+    ("int8", "int32", 900, 264, 512),               # integer accumulators
+])
+def test_epilogue_paths_agree_bit_for_bit(compute, kind, out_kind, m, n, k):
+    """C <- relu(alpha * A @ B + beta * C + bias) from a non-zero C: results stored from registers, through staging
+    boxes stored by TMA, and through boxes the epilogue warps move themselves (with the old C copied in ahead, and
+    with the old C read row by row) must be identical; one of them is checked against fp64."""
+    import torch
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(m * 7 + n)
+    if kind == "int8":
+        A = torch.randint(-4, 5, (m, k), generator=g, dtype=torch.int8).to(dev)
+        B = torch.randint(-4, 5, (n, k), generator=g, dtype=torch.int8).to(dev).t()
+        C0 = torch.randint(-100, 100, (m, n), generator=g, dtype=torch.int32).to(dev)
+        bias, alpha, beta = None, 1.0, 1.0
+    else:
+        dt = torch.bfloat16 if kind == "bfloat16" else torch.float16
+        odt = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}[out_kind]
+        A = torch.randn(m, k, generator=g).to(dt).to(dev)
+        B = (torch.randn(n, k, generator=g) / k ** 0.5).to(dt).to(dev).t()
+        C0 = torch.randn(m, n, generator=g).to(odt).to(dev)
+        bias, alpha, beta = torch.randn(n, generator=g).to(dev), 0.5, 2.0
+    results = {}
+    variants = {"registers": {"gemm.staged_store": 0}, "tma boxes": {"gemm.staged_store": 1},
+                "warp-moved boxes, C copied ahead": {"gemm.staged_store": 2, "gemm.c_in": 1},
+                "warp-moved boxes": {"gemm.staged_store": 2, "gemm.c_in": 0}}
+    for name, opts in variants.items():
+        C = C0.clone()
+        with rt.options(**opts):
+            # a grid of 8 CTAs makes every CTA walk several tiles, so that copies run ahead across tile boundaries
+            rt.gemm(A, B, C, bias=bias, alpha=alpha, beta=beta, relu=True, compute=compute, max_ctas=8 if m > 1024 else 0)
+        rt.synchronize()
+        results[name] = C
+    base = results["tma boxes"]
+    for name, C in results.items():
+        assert torch.equal(C, base), name
+    want = alpha * (A.double() @ B.double()) + beta * C0.double()
+    if bias is not None:
+        want = want + bias.double()
+    want = want.clamp_min(0)
+    if kind == "int8":
+        assert torch.equal(base.double(), want)
+    else:
+        scale = (alpha * (A.double().abs() @ B.double().abs()) + beta * C0.double().abs()).clamp_min(1.0)
+        assert ((base.double() - want).abs() / scale).max().item() <= 2e-2
