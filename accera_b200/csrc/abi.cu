@@ -310,7 +310,8 @@ int tensor_gemm_with_repacked_operands(const GemmLaunch& g0, const char** err)
 int tensor_gemm_split_k(const GemmLaunch& g, const char** err)
 {
     const accb_gemm_desc& d = g.d;
-    if (g.batch > 1 || g.n_extra_c > 0 || d.k < 2048) return 0;
+    const int forced = options().gemm_split_k;
+    if (g.batch > 1 || g.n_extra_c > 0 || forced == 0 || (forced < 0 && d.k < 2048)) return 0;
     const size_t es = type_bytes(d.a_type);
     const double slab = 128.0 / (double)es;                 // K elements per pipeline stage
     // Two tilings are candidates: the one the launch code would pick for the unsplit problem, and the widest tile
@@ -332,14 +333,14 @@ int tensor_gemm_split_k(const GemmLaunch& g, const char** err)
         const int64_t rows = c.two_sm ? 256 : 128;
         const int64_t tiles = ((d.m + rows - 1) / rows) * ((d.n + c.cols - 1) / c.cols);
         const int64_t units = c.two_sm ? g.num_sms / 2 : g.num_sms;
-        for (int64_t sl = units / tiles < 16 ? units / tiles : 16; sl >= 2; --sl) {
-            if (d.k % sl != 0) continue;
+        for (int64_t sl = forced >= 2 ? forced : (units / tiles < 16 ? units / tiles : 16); sl >= 2; --sl) {
+            if (d.k % sl != 0) { if (forced >= 2) break; continue; }
             const int64_t ks = d.k / sl;
-            if (ks < 512 || (ks * (int64_t)es) % 16 != 0) continue;
+            if ((ks < 512 && forced < 2) || (ks * (int64_t)es) % 16 != 0) { if (forced >= 2) break; continue; }
             const double rounds = (double)((tiles * sl + units - 1) / units);
             const double us = rounds * ((double)ks / slab) * (c.cols == 256 ? 0.28 : 0.22) + 7.0 +
                               (double)(sl + 1) * (double)d.m * (double)d.n * 4.0 / 4.0e6;
-            if (us < best_us * 0.9) { best_us = us; best_slices = (int)sl; best = c; }
+            if (us < best_us * 0.9 || (forced >= 2 && best_slices < 2)) { best_us = us; best_slices = (int)sl; best = c; }
             break;                                          // fewer slices of this tiling only cost more
         }
     }
@@ -635,6 +636,7 @@ int accb_set_option(const char* name, int64_t value)
     else if (n == "gemm.wait_limit_us") { if (value < 0 || value > 10000000) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.wait_limit_us is 0 (default) .. 10000000"); o.gemm_wait_limit_us = v; }
     else if (n == "gemm.test_drop_commit") o.gemm_test_drop_commit = v ? 1 : 0;
     else if (n == "gemm.pdl") o.gemm_pdl = v < 0 ? -1 : (v ? 1 : 0);
+    else if (n == "gemm.split_k") o.gemm_split_k = v < 0 ? -1 : (int)v;
     else if (n == "gemm.c_in") o.gemm_c_in = v < 0 ? -1 : (v ? 1 : 0);
     else if (n == "gemm.verbose") o.gemm_verbose = v ? 1 : 0;
     else if (n == "host_gemm.stage_chunks") { if (v < 0 || v > 256) return fail(ACCB_ERR_ARG, "accb_set_option: host_gemm.stage_chunks is 0 (default) .. 256"); o.host_stage_chunks = v; }

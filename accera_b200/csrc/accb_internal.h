@@ -45,6 +45,7 @@ struct Options {
     int gemm_wait_limit_us = 0;      // limit of every bounded device-side wait (default: one second)
     int gemm_test_drop_commit = 0;   // self-test: the MMA issuer leaves out the commit that completes the last accumulator
     int gemm_pdl = -1;               // programmatic dependent launch of the tensor-core GEMM: 0 off, 1 on
+    int gemm_split_k = -1;           // K slices of few-tile problems: -1 cost model, 0 never, n >= 2 exactly n when possible
     int gemm_c_in = -1;              // beta != 0: old C brought into the staging boxes by TMA loads (1) or read row by row (0)
     int gemm_verbose = 0;            // print the launch plan to stderr
     int host_stage_chunks = 0;       // row chunks of the staged host-pointer GEMM (default 16)
