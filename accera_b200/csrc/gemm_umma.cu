@@ -903,8 +903,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     using ACC = typename std::conditional<KIND == KIND_I8, int, float>::type;
     constexpr int kTmemCols = Plan::kTmemCols;
     constexpr int SMAX = Plan::kStages;
-    // stages in use: launches that load C through the staging boxes give the end of the ring to two more boxes per warp
-    const int S = p.c_in ? Plan::kCinStages : SMAX;
+    // c_in (the old C copied into the staging boxes ahead of use): a tile of up to two boxes per epilogue warp (128 columns
+    // of 2-byte results) fits the two boxes every launch has; wider tiles get a ring of four, for which the end of the
+    // operand ring is given up
+    constexpr int kCinBoxes = (BN * (int)sizeof(TC) / 128 <= 2) ? 2 : Plan::kCinBoxes;
+    const int S = (p.c_in && kCinBoxes > 2) ? Plan::kCinStages : SMAX;
     constexpr int kCtas = TWO_SM ? 2 : 1;
 
     extern __shared__ uint8_t smem_raw[];
@@ -1105,7 +1108,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int local = 0;
         bool ok = true;
         uint32_t store_count = 0;                    // TMA-store boxes this warp has issued (warp-uniform)
-        const uint32_t n_boxes = p.c_in ? (uint32_t)Plan::kCinBoxes : 2u;     // staging boxes of this warp
+        const uint32_t n_boxes = p.c_in ? (uint32_t)kCinBoxes : 2u;           // staging boxes of this warp
         uint8_t* store_stage = smem_gen + S * Plan::kStageBytes + (size_t)(warp - 2) * n_boxes * Plan::kStoreBoxBytes;
         // c_in: the old C of every box this warp will produce is copied (cp.async, 16 bytes per lane, 8 lanes per
         // 128-byte row, swizzled like the box) into the staging box the result is later written to, in the order in
@@ -1483,7 +1486,7 @@ int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap
         fprintf(stderr, "tcgen05 GEMM %lld x %lld x %lld x %d: %s tiles of %d columns, %d tiles on %d %s, pacing %d%%\n",
                 (long long)p.m, (long long)p.n, (long long)p.k, p.batch, TWO_SM ? "pair" : "single-CTA", BN, num_tiles, units,
                 TWO_SM ? "pairs" : "CTAs", p.pace_pct);
-    if (p.verbose && p.lsu_stage) fprintf(stderr, "  staged epilogue without TMA%s, %d operand stages\n", p.c_in ? ", old C copied in boxes ahead" : "", p.c_in ? Plan::kCinStages : Plan::kStages);
+    if (p.verbose && p.lsu_stage) fprintf(stderr, "  staged epilogue without TMA%s, %d operand stages\n", p.c_in ? ", old C copied in boxes ahead" : "", (p.c_in && BN * (int)sizeof(TC) / 128 > 2) ? Plan::kCinStages : Plan::kStages);
     if (p.verbose && p.n_replicas > 1)
         fprintf(stderr, "  %d replicas: %s\n", p.n_replicas, p.copy_ctas > 0 ? "forwarding CTAs" : p.peer_store ? "register stores from the epilogue" : "TMA stores from the epilogue");
     cfg.gridDim = dim3((unsigned)((units + copy_units) * (TWO_SM ? 2 : 1)));
@@ -1684,8 +1687,8 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
     // beta != 0 and a short K loop (up to 32 slabs of 128 bytes: K = 2048 for 16-bit operands): the epilogue of a
     // CTA's last tile is a large part of the launch, and most of it is waiting for the old C, read row by row when it
     // is needed.  There the epilogue warps copy the old C into their staging boxes boxes ahead (the first boxes of a
-    // tile while its K loop still runs) and move the boxes to C themselves; the extra boxes cost the operand ring one
-    // stage (two for narrow pair tiles).  Measured, C += A @ B in bf16, against the TMA-staged epilogue: 1024^3 10.0
+    // tile while its K loop still runs) and move the boxes to C themselves; for tiles wider than two boxes per warp
+    // the two extra boxes cost the operand ring one stage.  Measured, C += A @ B in bf16, against the TMA-staged epilogue: 1024^3 10.0
     // against 11.5 us, 2048^3 19.7 / 22.2, 3072 x 2048 x 1024 21.1 / 24.9; equal at K = 4096 (4096^3 116 / 116), 2 %
     // slower at 65536 x 8192 x 8192 (6.70 / 6.56 ms), which is why long K loops keep the TMA stores.
     {
