@@ -637,6 +637,7 @@ int accb_set_option(const char* name, int64_t value)
     else if (n == "gemm.test_drop_commit") o.gemm_test_drop_commit = v ? 1 : 0;
     else if (n == "gemm.pdl") o.gemm_pdl = v < 0 ? -1 : (v ? 1 : 0);
     else if (n == "gemm.split_k") o.gemm_split_k = v < 0 ? -1 : (int)v;
+    else if (n == "stream_kernels.pdl") o.stream_pdl = v < 0 ? -1 : (v ? 1 : 0);
     else if (n == "gemm.c_in") o.gemm_c_in = v < 0 ? -1 : (v ? 1 : 0);
     else if (n == "gemm.verbose") o.gemm_verbose = v ? 1 : 0;
     else if (n == "host_gemm.stage_chunks") { if (v < 0 || v > 256) return fail(ACCB_ERR_ARG, "accb_set_option: host_gemm.stage_chunks is 0 (default) .. 256"); o.host_stage_chunks = v; }

@@ -50,6 +50,7 @@ struct Options {
     int gemm_verbose = 0;            // print the launch plan to stderr
     int host_stage_chunks = 0;       // row chunks of the staged host-pointer GEMM (default 16)
     int reduce_rows_tpr = 0;         // reduce_mean over contiguous segments: threads per output (32, 64, 128 or 256)
+    int stream_pdl = -1;             // programmatic dependent launch of the reduce / gather / range kernels: 0 off, 1 on
 };
 Options& options();
 
@@ -78,6 +79,29 @@ struct GemmLaunch {
     int device;
     int num_sms;
 };
+
+// Launch with programmatic stream serialization: the kernel may be scheduled while the kernel before it in the
+// stream is still draining, which hides the launch and block-scheduling latency of back-to-back launches.  The
+// kernel must execute pdl_enter() before it touches global memory: that returns once everything earlier in the
+// stream has completed (at once for an ordinary predecessor).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = options().stream_pdl == 0 ? 0 : 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_enter()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+#endif
 
 // gemm_simt.cu: any supported type combination, any strides. Returns launches made (<0: ACCB_ERR_*).
 int launch_gemm_simt(const GemmLaunch& g, const char** err);

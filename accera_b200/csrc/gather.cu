@@ -26,6 +26,7 @@ gather_rows_vec_kernel(const uint4* __restrict__ data, const int64_t* __restrict
                        uint4* __restrict__ output, int64_t n_rows_in, int64_t vec_per_row,
                        int64_t chunks_per_row, int* __restrict__ status, int launch_id)
 {
+    pdl_enter();
     const int64_t row = blockIdx.x / chunks_per_row;
     const int64_t chunk = blockIdx.x % chunks_per_row;
     const int64_t src_row = indices[row];
@@ -55,6 +56,7 @@ __global__ void __launch_bounds__(kBlock)
 gather_elem_kernel(const T* __restrict__ data, const int64_t* __restrict__ indices, T* __restrict__ output,
                    int64_t d0, int64_t d1, int64_t n_idx, int axis, int64_t total, int* __restrict__ status, int launch_id)
 {
+    pdl_enter();
     for (int64_t e = (int64_t)blockIdx.x * kBlock + threadIdx.x; e < total; e += (int64_t)gridDim.x * kBlock) {
         int64_t src;
         bool ok;
@@ -81,9 +83,9 @@ cudaError_t launch_elem(const void* data, const int64_t* indices, void* output, 
 {
     int64_t blocks = (total + kBlock - 1) / kBlock;
     if (blocks > 148 * 64) blocks = 148 * 64;   // grid-stride beyond this
-    gather_elem_kernel<T><<<(unsigned)blocks, kBlock, 0, stream>>>((const T*)data, indices, (T*)output, d0, d1, n_idx,
-                                                                  axis, total, status, launch_id);
-    return cudaGetLastError();
+    const cudaError_t e = launch_pdl(gather_elem_kernel<T>, dim3((unsigned)blocks), dim3(kBlock), stream, (const T*)data, indices,
+                                     (T*)output, d0, d1, n_idx, axis, total, status, launch_id);
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace
@@ -102,9 +104,9 @@ int launch_gather(const void* data, int64_t d0, int64_t d1, const int64_t* indic
         const int64_t vpr = row_bytes / 16;
         const int64_t cpr = (vpr + kBlock * kUnroll - 1) / (kBlock * kUnroll);
         if (n_idx * cpr > 0x7fffffff) { *err = "gather: too many rows for this kernel's grid"; return ACCB_ERR_ARG; }
-        gather_rows_vec_kernel<<<(unsigned)(n_idx * cpr), kBlock, 0, stream>>>(
-            (const uint4*)data, indices, (uint4*)output, d0, vpr, cpr, status, launch_id);
-        e = cudaGetLastError();
+        e = launch_pdl(gather_rows_vec_kernel, dim3((unsigned)(n_idx * cpr)), dim3(kBlock), stream, (const uint4*)data, indices,
+                       (uint4*)output, d0, vpr, cpr, status, launch_id);
+        if (e == cudaSuccess) e = cudaGetLastError();
     } else {
         switch (elem_bytes) {
         case 1: e = launch_elem<uint8_t>(data, indices, output, d0, d1, n_idx, axis, total, status, launch_id, stream); break;

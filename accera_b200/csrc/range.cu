@@ -64,6 +64,7 @@ __device__ __forceinline__ int find_segment(const RangeTable& t, int64_t i)
 __global__ void __launch_bounds__(kBlock)
 range_fill_kernel(uint32_t* __restrict__ out, int64_t begin, int64_t end, const __grid_constant__ RangeTable table)
 {
+    pdl_enter();
     const int64_t block_base = (begin / kPerBlock + (int64_t)blockIdx.x) * kPerBlock;
     if (block_base >= end) return;
     const int s0 = find_segment(table, block_base < begin ? begin : block_base);
@@ -190,8 +191,9 @@ int launch_range_f32(int64_t n, float* output, float start, float delta, float* 
         const int64_t blocks = (end - (begin / kPerBlock) * kPerBlock + kPerBlock - 1) / kPerBlock;
         if (blocks > 0x7fffffff) { *err = "range: too many elements for this kernel's grid"; return ACCB_ERR_ARG; }
         if (blocks == 0) continue;
-        range_fill_kernel<<<(unsigned)blocks, kBlock, 0, stream>>>(reinterpret_cast<uint32_t*>(output), begin, end, table);
-        const cudaError_t e = cudaGetLastError();
+        cudaError_t e = launch_pdl(range_fill_kernel, dim3((unsigned)blocks), dim3(kBlock), stream, reinterpret_cast<uint32_t*>(output),
+                                   begin, end, table);
+        if (e == cudaSuccess) e = cudaGetLastError();
         if (e != cudaSuccess) { *err = cudaGetErrorString(e); return ACCB_ERR_CUDA; }
         ++launches;
     }

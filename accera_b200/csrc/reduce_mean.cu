@@ -118,6 +118,7 @@ __global__ void __launch_bounds__(kBlock)
 reduce_rows_kernel(const float* __restrict__ data, float* __restrict__ out, RowsParams p)
 {
     __shared__ float smem[kBlock / 32];
+    pdl_enter();
     constexpr int RPB = kBlock / TPR;
     const int t = threadIdx.x % TPR;
     const int64_t o = (int64_t)blockIdx.x * RPB + threadIdx.x / TPR;
@@ -172,6 +173,7 @@ reduce_rows_stream_kernel(const float* __restrict__ data, float* __restrict__ ou
                           int nv, float count)
 {
     __shared__ float smem[2][kBlock / 32];
+    pdl_enter();
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     float4 cur[VPT], nxt[VPT];
     auto load_row = [&](float4 (&v)[VPT], int64_t o) {
@@ -220,6 +222,7 @@ __global__ void __launch_bounds__(kBlock)
 reduce_cols_kernel(const float* __restrict__ data, float* __restrict__ out, ColsParams p)
 {
     __shared__ float4 smem[8][32];
+    pdl_enter();
     const int tx = threadIdx.x, ty = threadIdx.y;
     const int64_t o = blockIdx.x / p.col_blocks;
     const int vec = p.vec_ok ? 4 : 1;
@@ -281,6 +284,7 @@ __global__ void __launch_bounds__(kBlock)
 reduce_fold_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t n, int64_t nsplit,
                    int cols_layout, float count)
 {
+    pdl_enter();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float s = 0.0f;
@@ -421,14 +425,14 @@ int launch_reduce_mean(const float* data, int64_t d0, int64_t d1, int64_t d2, fl
                             nv <= 8 * kBlock && nv % (4 * kBlock) != 0 && r.n_out >= 2 * (int64_t)num_sms;
         if (streaming) {
             const unsigned g = (unsigned)(r.n_out < 8 * (int64_t)num_sms ? r.n_out : 8 * (int64_t)num_sms);
-            if (nv <= 4 * kBlock) reduce_rows_stream_kernel<4><<<g, kBlock, 0, stream>>>(data, dst, r.n_out, r.row_stride, (int)nv, r.count);
-            else reduce_rows_stream_kernel<8><<<g, kBlock, 0, stream>>>(data, dst, r.n_out, r.row_stride, (int)nv, r.count);
+            if (nv <= 4 * kBlock) (void)launch_pdl(reduce_rows_stream_kernel<4>, dim3(g), dim3(kBlock), stream, data, dst, r.n_out, r.row_stride, (int)nv, r.count);
+            else (void)launch_pdl(reduce_rows_stream_kernel<8>, dim3(g), dim3(kBlock), stream, data, dst, r.n_out, r.row_stride, (int)nv, r.count);
         } else
         switch (pl.tpr) {
-        case 32: reduce_rows_kernel<32><<<grid, kBlock, 0, stream>>>(data, dst, r); break;
-        case 64: reduce_rows_kernel<64><<<grid, kBlock, 0, stream>>>(data, dst, r); break;
-        case 128: reduce_rows_kernel<128><<<grid, kBlock, 0, stream>>>(data, dst, r); break;
-        default: reduce_rows_kernel<kBlock><<<grid, kBlock, 0, stream>>>(data, dst, r); break;
+        case 32: (void)launch_pdl(reduce_rows_kernel<32>, grid, dim3(kBlock), stream, data, dst, r); break;
+        case 64: (void)launch_pdl(reduce_rows_kernel<64>, grid, dim3(kBlock), stream, data, dst, r); break;
+        case 128: (void)launch_pdl(reduce_rows_kernel<128>, grid, dim3(kBlock), stream, data, dst, r); break;
+        default: (void)launch_pdl(reduce_rows_kernel<kBlock>, grid, dim3(kBlock), stream, data, dst, r); break;
         }
         ++launches;
     } else {
@@ -439,15 +443,15 @@ int launch_reduce_mean(const float* data, int64_t d0, int64_t d1, int64_t d2, fl
         if (gx * c.outer > 0x7fffffff) { *err = "reduce_mean: too many outputs"; return ACCB_ERR_ARG; }
         c.col_blocks = gx;
         dim3 grid((unsigned)(gx * c.outer), (unsigned)pl.nsplit);
-        reduce_cols_kernel<<<grid, dim3(32, 8), 0, stream>>>(data, dst, c);
+        (void)launch_pdl(reduce_cols_kernel, grid, dim3(32, 8), stream, data, dst, c);
         ++launches;
     }
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess && split) {
         const float inv = pl.rows ? pl.rp.count : pl.cp.count;
         const int64_t blocks = (pl.n_out + kBlock - 1) / kBlock;
-        reduce_fold_kernel<<<(unsigned)blocks, kBlock, 0, stream>>>(scratch, reduced, pl.n_out, pl.nsplit,
-                                                                   pl.rows ? 0 : 1, inv);
+        (void)launch_pdl(reduce_fold_kernel, dim3((unsigned)blocks), dim3(kBlock), stream, scratch, reduced, pl.n_out, pl.nsplit,
+                         pl.rows ? 0 : 1, inv);
         ++launches;
         e = cudaGetLastError();
     }

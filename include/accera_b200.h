@@ -291,6 +291,7 @@ const char* accb_version(void);
  *   "gemm.c_in"              -1 (choose) | 0 | 1      beta != 0 with warp-moved boxes: the old C is copied into the boxes ahead
  *                                                     of its use (1) or read row by row when needed (0)
  *   "gemm.verbose"           0 | 1                    print the launch plan to stderr
+ *   "stream_kernels.pdl"     -1 (on) | 0 | 1          programmatic dependent launch of the reduce_mean, gather and range kernels
  *   "host_gemm.stage_chunks" 0 (16) | 1..256          row chunks of the staged host-pointer GEMM
  *   "reduce.rows_threads_per_output"  0 (choose) | 32 | 64 | 128 | 256   reduce_mean over contiguous segments
  */
