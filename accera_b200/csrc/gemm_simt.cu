@@ -416,6 +416,7 @@ gemm_simt_f32_8x8_kernel(const float* __restrict__ A, const float* __restrict__ 
                          const float* __restrict__ bias, SimtParams p, SplitKParams sk)
 {
     constexpr int BM = 128, BN = 128, BK = 16, LDS_ = BM + 4;
+    pdl_enter();    // launched with programmatic stream serialization: wait for the stream's earlier work before any access
     // 64 KB: the k-tile buffers during the main loop (2 x 2 x 16 x 132 floats = 33 KB), the whole partial tile after it
     extern __shared__ __align__(16) float smem_f[];
     float (*As)[BK][LDS_] = reinterpret_cast<float (*)[BK][LDS_]>(smem_f);                       // As[2][k][m]
@@ -668,10 +669,14 @@ int launch_gemm_simt(const GemmLaunch& g, const char** err)
                 cfg.blockDim = dim3(256);
                 cfg.dynamicSmemBytes = kSmem;
                 cfg.stream = g.stream;
-                cudaLaunchAttribute attr[1];
+                cudaLaunchAttribute attr[2];
                 attr[0].id = cudaLaunchAttributeClusterDimension;
                 attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)sp.splits;
-                cfg.attrs = attr; cfg.numAttrs = 1;
+                // two of these CTAs fit an SM, so the next launch of a stream can be resident (and past its set-up)
+                // before this one has finished
+                attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[1].val.programmaticStreamSerializationAllowed = options().stream_pdl == 0 ? 0 : 1;
+                cfg.attrs = attr; cfg.numAttrs = 2;
                 e = cudaLaunchKernelEx(&cfg, gemm_simt_f32_8x8_kernel, (const float*)g.a, (const float*)g.b, (float*)g.c, g.bias, p, sk);
             }
         } else if (f32_rr_ok(g, p)) {
