@@ -580,3 +580,46 @@ def test_epilogue_paths_agree_bit_for_bit(compute, kind, out_kind, m, n, k):
     else:
         scale = (alpha * (A.double().abs() @ B.double().abs()) + beta * C0.double().abs()).clamp_min(1.0)
         assert ((base.double() - want).abs() / scale).max().item() <= 2e-2
+
+
+# ---------------------------------------------------------------------------
+# kernels that may be scheduled before their predecessor has finished still see its results
+# ---------------------------------------------------------------------------
+
+def test_back_to_back_launches_see_their_predecessors_results():
+    """Every kernel here is launched with programmatic stream serialization: its blocks may become resident while
+    the kernel before it in the stream is still running, and must not touch memory before that kernel is done.
+    A chain GEMM -> reduce_mean -> gather on one stream, with no synchronisation in between and fresh inputs every
+    round, is checked against the same chain computed by torch."""
+    import torch
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(5)
+    m, n, k = 2048, 1024, 512
+    idx = torch.randint(0, m, (300, 1), generator=g).to(dev)
+    for round_ in range(12):
+        A = torch.randn(m, k, generator=g).to(torch.float16).to(dev)
+        B = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.float16).to(dev).t()
+        C = torch.full((m, n), float(round_), device=dev)                  # fp32 result, beta = 1 from a known C
+        mean = torch.full((m,), float("nan"), device=dev)
+        rows = torch.full((300, 1, n), float("nan"), device=dev)
+        cols = torch.full((n,), float("nan"), device=dev)
+        rt.gemm(A, B, C, beta=1.0, relu=True, compute="tensor_preferred")
+        rt.reduce_mean_rank3(C.view(1, m, n), mean, [2])                    # reads what the GEMM wrote
+        rt.reduce_mean_rank3(C.view(1, m, n), cols, [1])                    # split reduction: two dependent launches
+        rt.gather_rank2(C, idx, rows, 0)
+        rt.gemm(A, B, C, beta=1.0, relu=False, compute="tensor_preferred")  # overwrites what the three kernels above read
+        rt.synchronize()
+        want_c = torch.relu(A.float() @ B.float() + float(round_))
+        scale = (A.float().abs() @ B.float().abs()).max().item() + round_
+        assert (mean - want_c.mean(dim=1)).abs().max().item() <= 2e-2 * scale
+        assert (cols - want_c.mean(dim=0)).abs().max().item() <= 2e-2 * scale
+        assert (rows.view(300, n) - want_c[idx.view(-1)]).abs().max().item() <= 2e-2 * scale
+        # the consumers read exactly the first GEMM's output, bit for bit: recompute them from a saved copy
+        C1 = torch.full((m, n), float(round_), device=dev)
+        rt.gemm(A, B, C1, beta=1.0, relu=True, compute="tensor_preferred")
+        rt.synchronize()
+        mean1 = torch.empty(m, device=dev)
+        rt.reduce_mean_rank3(C1.view(1, m, n), mean1, [2])
+        rt.synchronize()
+        assert torch.equal(mean, mean1)
+        assert torch.equal(rows.view(300, n), C1[idx.view(-1)])
