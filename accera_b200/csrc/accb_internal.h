@@ -34,7 +34,8 @@ int next_launch_id();
 // "choose as usual".
 struct Options {
     int gemm_tile_cols = 0;          // 128 | 256: accumulator columns per tile
-    int gemm_staged_store = -1;      // 0: epilogue stores straight from registers, 1: shared-memory staging + TMA stores
+    int gemm_staged_store = -1;      // epilogue: 0 stores straight from registers, 1 shared-memory staging + TMA stores,
+                                     // 2 staging boxes moved by the epilogue warps themselves
     int gemm_pace_pct = -1;          // tile-by-tile pacing of the persistent CTAs: 0 off, 1..100 on
     int gemm_group_m = 0;            // tile rows visited together
     int gemm_hint_a = 0, gemm_hint_b = 0;   // L2 eviction priority of the operand loads (1 evict-first, 2 evict-last)
@@ -46,7 +47,7 @@ struct Options {
     int gemm_test_drop_commit = 0;   // self-test: the MMA issuer leaves out the commit that completes the last accumulator
     int gemm_pdl = -1;               // programmatic dependent launch of the tensor-core GEMM: 0 off, 1 on
     int gemm_split_k = -1;           // K slices of few-tile problems: -1 cost model, 0 never, n >= 2 exactly n when possible
-    int gemm_c_in = -1;              // beta != 0: old C brought into the staging boxes by TMA loads (1) or read row by row (0)
+    int gemm_c_in = -1;              // beta != 0 with warp-moved boxes: old C copied into the boxes ahead of use (1) or read row by row (0)
     int gemm_verbose = 0;            // print the launch plan to stderr
     int host_stage_chunks = 0;       // row chunks of the staged host-pointer GEMM (default 16)
     int reduce_rows_tpr = 0;         // reduce_mean over contiguous segments: threads per output (32, 64, 128 or 256)

@@ -15,8 +15,9 @@
 // (accera/acc-translate/src/Target/Cpp/CppPrinterUtils.h:630-655), applied here
 // once per output tile after the whole K accumulation.
 //
-// Layout contract: A is K-contiguous (row-major M x K) and B is K-contiguous
-// (column-major K x N): both are "K-major" operands, loaded without transposition.
+// Layout contract: each operand is K-contiguous (row-major A, column-major B: "K-major", loaded without
+// transposition) or, for 16-bit and 8-bit types, M / N-contiguous (column-major A, row-major B: "MN-major"
+// shared-memory descriptors), with 16-byte aligned rows.
 //
 // Kernel structure (one CTA per SM, 192 threads, or CTA pairs with cta_group::2):
 //   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of a
@@ -26,7 +27,13 @@
 //               K=32 bytes per instruction), commits to the stage's "empty"
 //               mbarrier, and after the last K slab to the accumulator's "full" one
 //   warps 2..5  epilogue: tcgen05.ld the 128 x 256 accumulator (each warp its own 32
-//               TMEM lanes), scale / add C / bias / ReLU / convert, 16-byte stores
+//               TMEM lanes, the next 32 columns in flight while these are worked on),
+//               scale / add C / bias / ReLU / convert, then one of three ways out:
+//               shared-memory boxes stored by TMA (the default), boxes the warps move
+//               themselves with the old C copied in ahead of use (short K loops with
+//               beta != 0), or 16-byte stores straight from registers (column-major C)
+// A launch that writes C to several replicas (other GPUs' memory) can set its last
+// CTAs aside to forward finished tiles instead of computing (copy_tiles).
 // Two TMEM accumulators (2 x 256 columns) let the epilogue of tile i overlap the
 // main loop of tile i+1.  Tiles are visited in groups of rows so that the CTAs
 // running at the same time share A and B panels in L2.
