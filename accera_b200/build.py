@@ -19,7 +19,7 @@ OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(_PKG, "libaccera_b200.so")
 INCLUDE_DIR = os.path.join(os.path.dirname(_PKG), "include")
 
-SOURCES = ["abi.cu", "gemm_simt.cu", "gemm_umma.cu", "gemm_splitk.cu", "reduce_mean.cu", "gather.cu", "range.cu"]
+SOURCES = ["abi.cu", "gemm_simt.cu", "gemm_umma.cu", "gemm_splitk.cu", "repack.cu", "reduce_mean.cu", "gather.cu", "range.cu"]
 HEADERS = ["accb_internal.h", os.path.join(INCLUDE_DIR, "accera_b200.h")]
 
 NVCC_FLAGS = [

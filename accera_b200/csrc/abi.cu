@@ -237,8 +237,8 @@ namespace {
 int tensor_gemm_split_k(const GemmLaunch& g, const char** err);
 
 // An operand the tensor-core path cannot take only because its rows (or its base) are not 16-byte aligned - a
-// K of 30522 bf16 elements, say - is copied into a temporary with an aligned pitch (one pitched device-to-device
-// copy; rows past the matrix edge need no padding, TMA zero-fills them) and the GEMM runs on that.  The temporary comes
+// K of 30522 bf16 elements, say - is copied into a temporary with an aligned pitch (one kernel, repack.cu,
+// which also writes the zero padding of K; rows past the matrix edge need none, TMA zero-fills them) and the GEMM runs on that.  The temporary comes
 // from the stream-ordered allocator (cudaMallocAsync on the launch stream, freed on it right after the launch), so
 // nothing synchronises and concurrent streams do not share it.  Returns launches made, 0 when this does not apply
 // (the caller then uses the CUDA-core kernel), or a negative ACCB_ERR_*.
@@ -281,11 +281,10 @@ int tensor_gemm_with_repacked_operands(const GemmLaunch& g0, const char** err)
         const size_t new_pitch = ((size_t)new_width * es + 15) & ~(size_t)15;
         cudaError_t e = cudaMallocAsync(&tmp[i], new_pitch * (size_t)new_rows, g.stream);
         if (e != cudaSuccess) { (void)cudaGetLastError(); tmp[i] = nullptr; release(); return 0; }   // no memory to spare: CUDA-core kernel
-        if (k_new != d.k) e = cudaMemsetAsync(tmp[i], 0, new_pitch * (size_t)new_rows, g.stream);
-        if (e == cudaSuccess)
-            e = cudaMemcpy2DAsync(tmp[i], new_pitch, *o.base, (size_t)*o.pitch * es, (size_t)old_width * es, (size_t)old_rows,
-                                  cudaMemcpyDeviceToDevice, g.stream);
-        if (e != cudaSuccess) { *err = cudaGetErrorString(e); release(); return ACCB_ERR_CUDA; }
+        // one kernel copies the rows and writes the zero columns / rows of the padding
+        const int rc = launch_repack_rows(*o.base, *o.pitch * (int64_t)es, old_rows, old_width, (int)es, tmp[i], (int64_t)new_pitch,
+                                          new_rows, g.stream, err);
+        if (rc < 0) { release(); return rc; }
         *o.base = tmp[i];
         *o.pitch = (int64_t)(new_pitch / es);
     }

@@ -122,6 +122,10 @@ void gemm_umma_launch_geometry(const GemmLaunch& g, int want_two_sm, int32_t out
 int launch_splitk_reduce(const void* partial, int slices, const accb_gemm_desc& d, void* c, const float* bias,
                          cudaStream_t stream, const char** err);
 
+// repack.cu: copy of an operand into rows with a 16-byte aligned pitch, zero-padded (see the file)
+int launch_repack_rows(const void* src, int64_t src_pitch, int64_t rows, int64_t width, int elem_bytes, void* dst,
+                       int64_t dst_pitch, int64_t dst_rows, cudaStream_t stream, const char** err);
+
 // reduce_mean.cu
 // Scratch (fp32 partial sums) a launch needs for these dims, in bytes; 0 when the
 // single-pass kernels are used.
