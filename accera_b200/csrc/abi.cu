@@ -310,21 +310,23 @@ int tensor_gemm_split_k(const GemmLaunch& g, const char** err)
 {
     const accb_gemm_desc& d = g.d;
     const int forced = options().gemm_split_k;
-    if (g.batch > 1 || g.n_extra_c > 0 || forced == 0 || (forced < 0 && d.k < 2048)) return 0;
+    if (g.batch > 1 || g.n_extra_c > 0 || g.no_split_k || forced == 0 || (forced < 0 && d.k < 2048)) return 0;
     const size_t es = type_bytes(d.a_type);
     const double slab = 128.0 / (double)es;                 // K elements per pipeline stage
     // Two tilings are candidates: the one the launch code would pick for the unsplit problem, and the widest tile
     // (256 columns; a CTA pair when M spans more than one tile row).  For each, the largest slice count that fills
     // the machine, divides K exactly (a slice must not run into the next row of a K-contiguous operand), keeps
-    // every slice's start 16-byte aligned and leaves each slice at least 512 long.  Costs in microseconds from the
-    // measured stage times: 0.28 us per stage of a 256-column tile, 0.22 us of a 128-column one; the split adds a
-    // second launch and the partials' round trip through HBM (about 7 us + bytes at 4 TB/s).
+    // every slice's start 16-byte aligned and leaves each slice at least 512 long.  Costs in microseconds from
+    // measured launches of few-tile problems (64 x 320 x 2880, 512 x 512 x 8192, 1024 x 2048 x 4096): 0.33 us per stage
+    // of a 256-column tile, 0.27 us of a 128-column one (a lone tile per SM is bound by the latency of its loads, not
+    // by the tensor pipe); the split adds the reduction pass (about 3.5 us, launched so that it overlaps the tail of
+    // the GEMM) and the partials' round trip through memory (bytes at 4 TB/s).
     int plan_two = 0, plan_cols = 0;
     int64_t plan_tiles = 0, plan_rounds = 0;
     gemm_umma_tile_plan(g, d.m > 128 ? -1 : 0, &plan_two, &plan_cols, &plan_tiles, &plan_rounds);
     struct Cand { int two_sm, cols; };
     const Cand cands[2] = { { plan_two, plan_cols }, { d.m > 128 ? 1 : 0, 256 } };
-    const double unsplit_us = (double)plan_rounds * ((double)d.k / slab) * (plan_cols == 256 ? 0.28 : 0.22);
+    const double unsplit_us = (double)plan_rounds * ((double)d.k / slab) * (plan_cols == 256 ? 0.33 : 0.27);
     double best_us = unsplit_us;
     int best_slices = 1;
     Cand best = cands[0];
@@ -337,7 +339,7 @@ int tensor_gemm_split_k(const GemmLaunch& g, const char** err)
             const int64_t ks = d.k / sl;
             if ((ks < 512 && forced < 2) || (ks * (int64_t)es) % 16 != 0) { if (forced >= 2) break; continue; }
             const double rounds = (double)((tiles * sl + units - 1) / units);
-            const double us = rounds * ((double)ks / slab) * (c.cols == 256 ? 0.28 : 0.22) + 7.0 +
+            const double us = rounds * ((double)ks / slab) * (c.cols == 256 ? 0.33 : 0.27) + 3.5 +
                               (double)(sl + 1) * (double)d.m * (double)d.n * 4.0 / 4.0e6;
             if (us < best_us * 0.9 || (forced >= 2 && best_slices < 2)) { best_us = us; best_slices = (int)sl; best = c; }
             break;                                          // fewer slices of this tiling only cost more
@@ -443,6 +445,7 @@ int pipelined_host_gemm(DeviceState& s, GemmLaunch g, const void* a, const void*
         part.a = (const char*)s.slot[0] + off_a;
         part.c = (char*)s.slot[2] + off_c;
         part.stream = st;
+        part.no_split_k = true;          // the chunks are a way of moving the data: the result must not depend on them
         const char* err = "";
         const int n = dispatch_gemm(part, &err);
         if (n < 0) {

@@ -74,6 +74,7 @@ struct GemmLaunch {
     int64_t batch = 1;
     int64_t a_batch_stride = 0, b_batch_stride = 0, c_batch_stride = 0;
     int force_tile_cols = 0;   // tensor-core path: 128 or 256 accumulator columns per tile instead of the cost model's choice
+    bool no_split_k = false;   // row chunks of one staged host-pointer GEMM: every chunk must round like a single launch would
     cudaStream_t stream;
     int* status;       // device pointer to kStatusWords ints
     int launch_id;     // attribution of device-side failures (next_launch_id)

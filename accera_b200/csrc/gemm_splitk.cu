@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(256)
 splitk_reduce_f32_kernel(const float* __restrict__ partial, int slices, int64_t m, int64_t n, TC* __restrict__ C, int64_t cs0,
                          int64_t cs1, float alpha, float beta, const float* __restrict__ bias, int relu)
 {
+    pdl_enter();    // may be resident while the launch that writes the partial sums still runs: wait for it before reading
     const int64_t groups_per_row = (n + 3) / 4;
     const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (g >= m * groups_per_row) return;
@@ -56,6 +57,7 @@ __global__ void __launch_bounds__(256)
 splitk_reduce_s32_kernel(const int* __restrict__ partial, int slices, int64_t m, int64_t n, int* __restrict__ C, int64_t cs0,
                          int64_t cs1, int add_c, int relu)
 {
+    pdl_enter();
     const int64_t groups_per_row = (n + 3) / 4;
     const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (g >= m * groups_per_row) return;
@@ -96,20 +98,20 @@ int launch_splitk_reduce(const void* partial, int slices, const accb_gemm_desc& 
     const unsigned gsz = (unsigned)blocks;
     switch (d.c_type) {
     case ACCB_F32:
-        splitk_reduce_f32_kernel<float><<<gsz, 256, 0, stream>>>((const float*)partial, slices, d.m, d.n, (float*)c, d.c_stride[0],
-                                                                 d.c_stride[1], d.alpha, d.beta, bias, relu);
+        (void)launch_pdl(splitk_reduce_f32_kernel<float>, dim3(gsz), dim3(256), stream, (const float*)partial, slices, d.m, d.n, (float*)c,
+                         d.c_stride[0], d.c_stride[1], d.alpha, d.beta, bias, relu);
         break;
     case ACCB_F16:
-        splitk_reduce_f32_kernel<__half><<<gsz, 256, 0, stream>>>((const float*)partial, slices, d.m, d.n, (__half*)c, d.c_stride[0],
-                                                                  d.c_stride[1], d.alpha, d.beta, bias, relu);
+        (void)launch_pdl(splitk_reduce_f32_kernel<__half>, dim3(gsz), dim3(256), stream, (const float*)partial, slices, d.m, d.n, (__half*)c,
+                         d.c_stride[0], d.c_stride[1], d.alpha, d.beta, bias, relu);
         break;
     case ACCB_BF16:
-        splitk_reduce_f32_kernel<__nv_bfloat16><<<gsz, 256, 0, stream>>>((const float*)partial, slices, d.m, d.n, (__nv_bfloat16*)c,
-                                                                         d.c_stride[0], d.c_stride[1], d.alpha, d.beta, bias, relu);
+        (void)launch_pdl(splitk_reduce_f32_kernel<__nv_bfloat16>, dim3(gsz), dim3(256), stream, (const float*)partial, slices, d.m, d.n,
+                         (__nv_bfloat16*)c, d.c_stride[0], d.c_stride[1], d.alpha, d.beta, bias, relu);
         break;
     case ACCB_S32:
-        splitk_reduce_s32_kernel<<<gsz, 256, 0, stream>>>((const int*)partial, slices, d.m, d.n, (int*)c, d.c_stride[0], d.c_stride[1],
-                                                          d.beta != 0.0f, relu);
+        (void)launch_pdl(splitk_reduce_s32_kernel, dim3(gsz), dim3(256), stream, (const int*)partial, slices, d.m, d.n, (int*)c, d.c_stride[0],
+                         d.c_stride[1], (int)(d.beta != 0.0f), relu);
         break;
     default:
         *err = "split-K reduction: unsupported output type";

@@ -623,3 +623,24 @@ def test_back_to_back_launches_see_their_predecessors_results():
         rt.synchronize()
         assert torch.equal(mean, mean1)
         assert torch.equal(rows.view(300, n), C1[idx.view(-1)])
+
+
+def test_fp32_operands_with_unaligned_rows_take_the_tf32_path_when_asked():
+    """4-byte elements through the same repacking: fp32 rows of 1001 elements (4004 bytes) are not 16-byte aligned;
+    "tensor_preferred" repacks them and computes in TF32 (tolerance 1e-3 of the |A| @ |B| scale, the reference's
+    fp32-as-TF32 bar)."""
+    import torch
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device="cpu").manual_seed(17)
+    m, n, k = 300, 264, 1001
+    A = torch.randn(m, k, generator=g).to(dev)
+    B = (torch.randn(n, k, generator=g) / k ** 0.5).to(dev).t()        # K-contiguous, rows of 4004 bytes
+    C0 = torch.randn(m, n, generator=g).to(dev)
+    C = C0.clone()
+    before = rt.launch_count()
+    rt.gemm(A, B, C, beta=1.0, relu=True, compute="tensor_preferred")
+    rt.synchronize()
+    assert rt.launch_count() - before >= 3                              # two repacks and the GEMM
+    want = torch.relu(A.double() @ B.double() + C0.double())
+    scale = A.double().abs() @ B.double().abs() + C0.double().abs()
+    assert ((C.double() - want).abs() / scale).max().item() <= 1e-3
