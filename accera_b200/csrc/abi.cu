@@ -638,6 +638,7 @@ int accb_set_option(const char* name, int64_t value)
     else if (n == "gemm.wait_limit_us") { if (value < 0 || value > 10000000) return fail(ACCB_ERR_ARG, "accb_set_option: gemm.wait_limit_us is 0 (default) .. 10000000"); o.gemm_wait_limit_us = v; }
     else if (n == "gemm.test_drop_commit") o.gemm_test_drop_commit = v ? 1 : 0;
     else if (n == "gemm.pdl") o.gemm_pdl = v < 0 ? -1 : (v ? 1 : 0);
+    else if (n == "gemm.epi_warps") o.gemm_epi_warps = (v == 4) ? 4 : (v == 8 ? 8 : 0);
     else if (n == "gemm.split_k") o.gemm_split_k = v < 0 ? -1 : (int)v;
     else if (n == "stream_kernels.pdl") o.stream_pdl = v < 0 ? -1 : (v ? 1 : 0);
     else if (n == "gemm.c_in") o.gemm_c_in = v < 0 ? -1 : (v ? 1 : 0);

@@ -46,6 +46,7 @@ struct Options {
     int gemm_wait_limit_us = 0;      // limit of every bounded device-side wait (default: one second)
     int gemm_test_drop_commit = 0;   // self-test: the MMA issuer leaves out the commit that completes the last accumulator
     int gemm_pdl = -1;               // programmatic dependent launch of the tensor-core GEMM: 0 off, 1 on
+    int gemm_epi_warps = 0;          // epilogue with warp-moved boxes: 0 / 8 = eight epilogue warps, 4 = four
     int gemm_split_k = -1;           // K slices of few-tile problems: -1 cost model, 0 never, n >= 2 exactly n when possible
     int gemm_c_in = -1;              // beta != 0 with warp-moved boxes: old C copied into the boxes ahead of use (1) or read row by row (0)
     int gemm_verbose = 0;            // print the launch plan to stderr

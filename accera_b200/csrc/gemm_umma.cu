@@ -60,8 +60,9 @@ constexpr int kBlockM = 128;          // accumulator rows per CTA (TMEM lanes)
 constexpr int kBlockN = 256;          // widest accumulator tile (UMMA N); kernels are also built for 128 columns
 constexpr int kSlabBytes = 128;       // bytes of K per stage row: one 128B swizzle atom
 constexpr int kMmaKBytes = 32;        // bytes of K one tcgen05.mma consumes
-constexpr int kThreads = 192;
+constexpr int kThreads = 192;          // producer warp, MMA warp, four epilogue warps
 constexpr int kEpiWarps = 4;
+constexpr int kThreadsWide = 320;      // with eight epilogue warps (launches whose epilogue shows: see UmmaParams::epi_warps)
 constexpr uint32_t kPeerMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address (rank 0 of a pair)
 
 enum { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2 };
@@ -134,6 +135,10 @@ struct UmmaParams {
                             // load of C queues behind the operand loads of several pipeline stages
     int c_in;               // lsu_stage with beta != 0: the old C is copied into the staging boxes boxes ahead (cp.async,
                             // also across tiles) instead of being read row by row when it is needed
+    int epi_warps;          // 4, or 8 with lsu_stage: two warps per TMEM lane quarter, each taking half of the tile's columns.
+                            // An epilogue warp is alone on its scheduler and bound by instruction latency (measured 0.6 us
+                            // per 32-column chunk); where a CTA's last epilogue is a large part of the launch, a second
+                            // warp per scheduler halves it
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -901,7 +906,7 @@ __device__ void copy_tiles(const UmmaParams& p, const CReplicaMaps& cmaps, uint3
 }
 
 template <int KIND, typename TC, bool TWO_SM, int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreadsWide, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CReplicaMaps cmaps, TC* __restrict__ C, const float* __restrict__ bias,
                  const UmmaParams p)
@@ -913,8 +918,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // c_in (the old C copied into the staging boxes ahead of use): a tile of up to two boxes per epilogue warp (128 columns
     // of 2-byte results) fits the two boxes every launch has; wider tiles get a ring of four, for which the end of the
     // operand ring is given up
-    constexpr int kCinBoxes = (BN * (int)sizeof(TC) / 128 <= 2) ? 2 : Plan::kCinBoxes;
-    const int S = (p.c_in && kCinBoxes > 2) ? Plan::kCinStages : SMAX;
+    // boxes of one tile that one epilogue warp produces, and the staging boxes it gets: all epilogue warps together have
+    // kStoreBytes (every launch) or twice that (c_in with tiles wider than that, at the price of operand stages)
+    const int halves = p.epi_warps / kEpiWarps;                              // 1, or 2: each warp takes half of the columns
+    const int boxes_per_warp_tile = BN * (int)sizeof(TC) / 128 / halves;
+    const int base_boxes = 2 / halves;                                       // boxes per warp inside kStoreBytes
+    const int cin_boxes = (boxes_per_warp_tile <= base_boxes) ? base_boxes : 2 * base_boxes;
+    const int S = (p.c_in && cin_boxes > base_boxes) ? Plan::kCinStages : SMAX;
     constexpr int kCtas = TWO_SM ? 2 : 1;
 
     extern __shared__ uint8_t smem_raw[];
@@ -971,7 +981,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tmem_full_bar(b), 1);                    // one tcgen05.commit
-            mbar_init(tmem_empty_bar(b), kEpiWarps * kCtas);   // one arrive per epilogue warp (of both CTAs)
+            mbar_init(tmem_empty_bar(b), (uint32_t)(p.epi_warps * kCtas));   // one arrive per epilogue warp (of both CTAs)
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -1115,14 +1125,15 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int local = 0;
         bool ok = true;
         uint32_t store_count = 0;                    // TMA-store boxes this warp has issued (warp-uniform)
-        const uint32_t n_boxes = p.c_in ? (uint32_t)kCinBoxes : 2u;           // staging boxes of this warp
-        uint8_t* store_stage = smem_gen + S * Plan::kStageBytes + (size_t)(warp - 2) * n_boxes * Plan::kStoreBoxBytes;
+        const int ew = warp - 2;                      // epilogue warp 0 .. epi_warps - 1
+        const int half = ew >> 2;                     // eight warps: warps 4 .. 7 take the second half of the tile's columns
+        const uint32_t n_boxes = (uint32_t)(p.c_in ? cin_boxes : base_boxes);  // staging boxes of this warp
+        uint8_t* store_stage = smem_gen + S * Plan::kStageBytes + (size_t)ew * n_boxes * Plan::kStoreBoxBytes;
         // c_in: the old C of every box this warp will produce is copied (cp.async, 16 bytes per lane, 8 lanes per
         // 128-byte row, swizzled like the box) into the staging box the result is later written to, in the order in
         // which the boxes are produced and as far ahead as the ring allows - the first boxes of the next tile while
         // this warp still waits for that tile's accumulator.  The n-th copy and the n-th result use box n % n_boxes.
         constexpr int kBoxCols = 128 / (int)sizeof(TC);          // columns per staging box
-        constexpr int kBoxesPerTile = BN / kBoxCols;
         constexpr int kPerVec = 16 / (int)sizeof(TC);
         const int vu = lane & 7, vr4 = lane >> 3;                // this lane's 16-byte unit and row (mod 4) in box moves
         uint32_t cin_issued = 0;                     // boxes whose copy has been issued (warp-uniform)
@@ -1136,7 +1147,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     cin_row0 = (int64_t)(tm * kCtas + (int)rank) * kBlockM + q * 32;
                     cin_col_tile = (int64_t)tn * BN;
                 }
-                const int64_t box_col0 = cin_col_tile + (int64_t)cin_box * kBoxCols;
+                const int64_t box_col0 = cin_col_tile + (int64_t)(half * boxes_per_warp_tile + cin_box) * kBoxCols;
                 if (cin_row0 < p.m && box_col0 < p.n) {
                     uint8_t* dst_box = store_stage + (size_t)(cin_issued % n_boxes) * Plan::kStoreBoxBytes;
                     const int64_t col = box_col0 + (int64_t)vu * kPerVec;
@@ -1153,7 +1164,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     asm volatile("cp.async.commit_group;" ::: "memory");
                     ++cin_issued;
                 }
-                if (++cin_box == kBoxesPerTile) { cin_box = 0; cin_t += num_units; }
+                if (++cin_box == boxes_per_warp_tile) { cin_box = 0; cin_t += num_units; }
             }
         };
         if (p.c_in) cin_issue_upto(n_boxes);
@@ -1267,28 +1278,21 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     }
                 }
             };
-            // The accumulator is read 32 columns at a time, the next chunk's tcgen05.ld in flight while this one is
-            // worked on (two register sets).
+            // this warp's share of the accumulator, 32 columns at a time
             {
-                uint32_t acc0[32], acc1[32];
-                tmem_ld32(taddr, acc0);
+                const int per_half = (BN / 32) / halves;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; c += 2) {
-                    tmem_wait_ld(acc0);
-                    tmem_ld32(taddr + (uint32_t)((c + 1) * 32), acc1);
-                    process_chunk(c, acc0);
-                    tmem_wait_ld(acc1);
-                    if (c + 2 < BN / 32) {
-                        tmem_ld32(taddr + (uint32_t)((c + 2) * 32), acc0);
-                    } else {
-                        // the whole accumulator is in registers: hand it back to the MMA issuer before the last chunk's work
-                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(TWO_SM ? (tmem_empty_bar(buf) & kPeerMask) : tmem_empty_bar(buf));
-                    }
-                    process_chunk(c + 1, acc1);
+                for (int c = half * per_half; c < (half + 1) * per_half; ++c) {
+                    uint32_t acc[32];
+                    tmem_ld32(taddr + (uint32_t)(c * 32), acc);
+                    tmem_wait_ld(acc);
+                    process_chunk(c, acc);
                 }
             }
+            // this warp has drained its part of the accumulator: hand it back to the MMA issuer
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(TWO_SM ? (tmem_empty_bar(buf) & kPeerMask) : tmem_empty_bar(buf));
             if (p.copy_ctas > 0 && lane == 0) {
                 // this warp's part of the tile is on its way to C: once the stores have completed, publish it to
                 // the forwarding CTAs (TMA writes belong to the async proxy, the readers use ordinary loads)
@@ -1413,6 +1417,18 @@ bool c_tma_storable(const accb_gemm_desc& d, const void* c)
            (reinterpret_cast<uintptr_t>(c) & 15) == 0;
 }
 
+// Launches whose epilogue shows - a K loop of up to 32 slabs of 128 bytes (K = 2048 for 16-bit operands) - and whose C
+// can be moved box by box (row-major, 16-byte aligned rows and row ends, one problem, no replicas) take the epilogue
+// with warp-moved boxes and eight epilogue warps.
+bool short_k_epilogue(const GemmLaunch& g)
+{
+    const accb_gemm_desc& d = g.d;
+    const int64_t slabs = (d.k * elem_size(d.a_type) + kSlabBytes - 1) / kSlabBytes;
+    const bool c_ok = d.c_stride[1] == 1 && (d.c_stride[0] * elem_size(d.c_type)) % 16 == 0 &&
+                      (reinterpret_cast<uintptr_t>(g.c) & 15) == 0 && ((d.n * elem_size(d.c_type)) % 16) == 0;
+    return c_ok && g.batch <= 1 && g.n_extra_c == 0 && slabs <= 32;
+}
+
 uint32_t make_idesc(int a_type, int b_type, bool int_acc, bool f16_out_acc, int m, int n, bool a_mn = false, bool b_mn = false)
 {
     auto fmt = [](int t) -> uint32_t {
@@ -1440,7 +1456,7 @@ int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap
     using Plan = SmemPlan<TWO_SM, BN>;
     auto kernel = gemm_umma_kernel<KIND, TC, TWO_SM, BN>;
     cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(32u * (2u + (unsigned)p.epi_warps));
     cfg.dynamicSmemBytes = Plan::kTotal;
     cfg.stream = g.stream;
     cudaLaunchAttribute attr[2];
@@ -1494,6 +1510,7 @@ int launch_variant(const GemmLaunch& g, const CUtensorMap& ma, const CUtensorMap
                 (long long)p.m, (long long)p.n, (long long)p.k, p.batch, TWO_SM ? "pair" : "single-CTA", BN, num_tiles, units,
                 TWO_SM ? "pairs" : "CTAs", p.pace_pct);
     if (p.verbose && p.lsu_stage) fprintf(stderr, "  staged epilogue without TMA%s, %d operand stages\n", p.c_in ? ", old C copied in boxes ahead" : "", (p.c_in && BN * (int)sizeof(TC) / 128 > 2) ? Plan::kCinStages : Plan::kStages);
+    if (p.verbose) fprintf(stderr, "  %d epilogue warps\n", p.epi_warps);
     if (p.verbose && p.n_replicas > 1)
         fprintf(stderr, "  %d replicas: %s\n", p.n_replicas, p.copy_ctas > 0 ? "forwarding CTAs" : p.peer_store ? "register stores from the epilogue" : "TMA stores from the epilogue");
     cfg.gridDim = dim3((unsigned)((units + copy_units) * (TWO_SM ? 2 : 1)));
@@ -1579,7 +1596,7 @@ void gemm_umma_launch_geometry(const GemmLaunch& g, int want_two_sm, int32_t out
         else { smem = SmemPlan<false, 128>::kTotal; stages = SmemPlan<false, 128>::kStages; }
     }
     out[0] = (int32_t)(units * per); out[1] = 1; out[2] = 1;
-    out[3] = kThreads; out[4] = 1; out[5] = 1;
+    out[3] = short_k_epilogue(g) ? kThreadsWide : kThreads; out[4] = 1; out[5] = 1;
     out[6] = smem;
     out[7] = stages;
 }
@@ -1691,20 +1708,24 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
         p.peer_store = (g.n_extra_c > 0 && vec_rows && (o.gemm_peer_store < 0 ? kPeerStoreDefault : o.gemm_peer_store)) ? 1 : 0;
     }
     p.launch_id = g.launch_id;
-    // beta != 0 and a short K loop (up to 32 slabs of 128 bytes: K = 2048 for 16-bit operands): the epilogue of a
-    // CTA's last tile is a large part of the launch, and most of it is waiting for the old C, read row by row when it
-    // is needed.  There the epilogue warps copy the old C into their staging boxes boxes ahead (the first boxes of a
-    // tile while its K loop still runs) and move the boxes to C themselves; for tiles wider than two boxes per warp
-    // the two extra boxes cost the operand ring one stage.  Measured, C += A @ B in bf16, against the TMA-staged epilogue: 1024^3 10.0
-    // against 11.5 us, 2048^3 19.7 / 22.2, 3072 x 2048 x 1024 21.1 / 24.9; equal at K = 4096 (4096^3 116 / 116), 2 %
-    // slower at 65536 x 8192 x 8192 (6.70 / 6.56 ms), which is why long K loops keep the TMA stores.
+    // A short K loop (up to 32 slabs of 128 bytes: K = 2048 for 16-bit operands): the epilogue of a CTA's last tile is a
+    // large part of the launch, and with several tiles per CTA the epilogue, not the K loop, sets the pace.  Timestamps
+    // inside the kernel (1024^3 bf16, C += A @ B: 1.5 us from the start to the first operands, 4.6 us of K loop, 2.6 us
+    // of epilogue for 128 columns) show an epilogue warp, alone on its scheduler, bound by instruction latency.  Such
+    // launches get eight epilogue warps, two per TMEM lane quarter, each taking half of the tile's columns; the warps
+    // move their staging boxes to C themselves and, with beta != 0, copy the old C into them boxes ahead (the first
+    // boxes of a tile while its K loop still runs) instead of reading it row by row when it is needed; for tiles wider
+    // than the boxes every launch has, the extra boxes cost the operand ring one stage.  Measured, C += A @ B in bf16,
+    // against the first epilogue (four warps, TMA-stored boxes): 1024^3 9.9 against 12.0 us, 2048^3 18.1 / 23.0,
+    // 3072 x 2048 x 1024 18.0 / 26.1, 4096 x 4096 x 1024 37.1 / 45.5 (fp32 results 40.3 / 68.9); with beta = 0
+    // 4096 x 4096 x 1024 28.7 / 32.7.  At K = 4096 it is equal or slower (4096^3 120 / 119) and 2 % slower at
+    // 65536 x 8192 x 8192, which is why long K loops keep four warps and the TMA stores.
     {
-        const int64_t slabs = (d.k * elem_size(d.a_type) + kSlabBytes - 1) / kSlabBytes;
         const Options& o = options();
         const bool can = p.tma_store && g.n_extra_c == 0 && ((d.n * elem_size(d.c_type)) % 16) == 0;
-        const bool short_k = slabs <= 32;
-        if (can && (o.gemm_staged_store == 2 || (o.gemm_staged_store < 0 && short_k && d.beta != 0.0f))) { p.lsu_stage = 1; p.tma_store = 0; }
+        if (can && (o.gemm_staged_store == 2 || (o.gemm_staged_store < 0 && short_k_epilogue(g)))) { p.lsu_stage = 1; p.tma_store = 0; }
         p.c_in = (p.lsu_stage && d.beta != 0.0f && (o.gemm_c_in >= 0 ? o.gemm_c_in : 1)) ? 1 : 0;
+        p.epi_warps = (p.lsu_stage && o.gemm_epi_warps != 4) ? 2 * kEpiWarps : kEpiWarps;
     }
     for (int r = 0; r < kMaxReplicas - 1; ++r) p.peer_c[r] = r < g.n_extra_c ? g.extra_c[r] : nullptr;
     // Forwarding CTAs: with three or more replicas to feed, the bytes leaving for other GPUs are a large share of

@@ -287,6 +287,7 @@ const char* accb_version(void);
  *                                                     ACCB_ERR_TIMEOUT (no fault, no trap; the context stays usable)
  *   "gemm.pdl"               -1 (on) | 0 | 1          programmatic dependent launch: the next GEMM of a stream is scheduled
  *                                                     and sets itself up while the previous kernel still runs
+ *   "gemm.epi_warps"         0 (choose) | 4 | 8       epilogue warps of a launch with warp-moved boxes
  *   "gemm.split_k"           -1 (choose) | 0 | n      K slices of a few-tile problem: cost model, never, or exactly n when n divides K
  *   "gemm.c_in"              -1 (choose) | 0 | 1      beta != 0 with warp-moved boxes: the old C is copied into the boxes ahead
  *                                                     of its use (1) or read row by row when needed (0)

@@ -541,7 +541,8 @@ def test_few_tiles_and_a_long_k_are_split_along_k(kind, out_kind, m, n, k, a_ord
 def test_epilogue_paths_agree_bit_for_bit(compute, kind, out_kind, m, n, k):
     """C <- relu(alpha * A @ B + beta * C + bias) from a non-zero C: results stored from registers, through staging
     boxes stored by TMA, and through boxes the epilogue warps move themselves (with the old C copied in ahead, and
-    with the old C read row by row) must be identical; one of them is checked against fp64."""
+    with the old C read row by row; with eight epilogue warps and with four) must be identical; one of them is checked
+    against fp64."""
     import torch
     dev = torch.device("cuda:0")
     g = torch.Generator(device="cpu").manual_seed(m * 7 + n)
@@ -560,7 +561,9 @@ def test_epilogue_paths_agree_bit_for_bit(compute, kind, out_kind, m, n, k):
     results = {}
     variants = {"registers": {"gemm.staged_store": 0}, "tma boxes": {"gemm.staged_store": 1},
                 "warp-moved boxes, C copied ahead": {"gemm.staged_store": 2, "gemm.c_in": 1},
-                "warp-moved boxes": {"gemm.staged_store": 2, "gemm.c_in": 0}}
+                "warp-moved boxes": {"gemm.staged_store": 2, "gemm.c_in": 0},
+                "warp-moved boxes, C copied ahead, four epilogue warps": {"gemm.staged_store": 2, "gemm.c_in": 1, "gemm.epi_warps": 4},
+                "warp-moved boxes, four epilogue warps": {"gemm.staged_store": 2, "gemm.c_in": 0, "gemm.epi_warps": 4}}
     for name, opts in variants.items():
         C = C0.clone()
         with rt.options(**opts):

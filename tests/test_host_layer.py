@@ -449,12 +449,13 @@ def test_gpu_target_functions_are_host_callable_and_record_the_true_launch(tmp_p
     meta = host.auxiliary["accera_b200"]
     assert meta["device_function"] == fn.name + "__gpu__" and meta["runtime"] == "CUDA" and meta["kernel"] == "gemm_umma_kernel"
     want = runtime.gemm_launch_geometry(512, 512, 512, in_type="float16", compute="tensor_preferred")
-    assert meta["launch_parameters"] == want["grid"] + want["block"] and meta["launch_parameters"][3:] == [192, 1, 1]
+    # a short K loop: the launch with eight epilogue warps (320 threads); the long one below keeps four (192)
+    assert meta["launch_parameters"] == want["grid"] + want["block"] and meta["launch_parameters"][3:] == [320, 1, 1]
     assert meta["dynamic_shared_mem_bytes"] == want["dynamic_shared_mem_bytes"] > 190000
     # the geometry is the variant's own: 16 single-CTA tiles of 128 columns here, 74 CTA pairs on the big problem
     assert meta["launch_parameters"][0] == 16 and meta["tile_cols"] == 128 and meta["cta_pairs"] is False
     bmeta = hf.function_map[big.name].auxiliary["accera_b200"]
-    assert bmeta["launch_parameters"][:3] == [148, 1, 1] and bmeta["cta_pairs"] is True and bmeta["tile_cols"] == 256
+    assert bmeta["launch_parameters"] == [148, 1, 1, 192, 1, 1] and bmeta["cta_pairs"] is True and bmeta["tile_cols"] == 256
     assert bmeta["tiles"] == 8192
     assert hf.target.required.gpu.model == "NVidia B200" and hf.target.required.gpu.runtime == "CUDA"
     _, fns = hat.load(hf.path)
