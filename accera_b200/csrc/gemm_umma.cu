@@ -1417,16 +1417,17 @@ bool c_tma_storable(const accb_gemm_desc& d, const void* c)
            (reinterpret_cast<uintptr_t>(c) & 15) == 0;
 }
 
-// Launches whose epilogue shows - a K loop of up to 32 slabs of 128 bytes (K = 2048 for 16-bit operands) - and whose C
-// can be moved box by box (row-major, 16-byte aligned rows and row ends, one problem, no replicas) take the epilogue
-// with warp-moved boxes and eight epilogue warps.
-bool short_k_epilogue(const GemmLaunch& g)
+// Launches whose epilogue shows - a K loop of up to 32 slabs of 128 bytes (K = 2048 for 16-bit operands), or up to 64
+// when every CTA has one tile only, so that nothing overlaps its epilogue - and whose C can be moved box by box
+// (row-major, 16-byte aligned rows and row ends, one problem, no replicas) take the epilogue with warp-moved boxes and
+// eight epilogue warps.
+bool short_k_epilogue(const GemmLaunch& g, bool one_round)
 {
     const accb_gemm_desc& d = g.d;
     const int64_t slabs = (d.k * elem_size(d.a_type) + kSlabBytes - 1) / kSlabBytes;
     const bool c_ok = d.c_stride[1] == 1 && (d.c_stride[0] * elem_size(d.c_type)) % 16 == 0 &&
                       (reinterpret_cast<uintptr_t>(g.c) & 15) == 0 && ((d.n * elem_size(d.c_type)) % 16) == 0;
-    return c_ok && g.batch <= 1 && g.n_extra_c == 0 && slabs <= 32;
+    return c_ok && g.batch <= 1 && g.n_extra_c == 0 && (slabs <= 32 || (one_round && slabs <= 64));
 }
 
 uint32_t make_idesc(int a_type, int b_type, bool int_acc, bool f16_out_acc, int m, int n, bool a_mn = false, bool b_mn = false)
@@ -1585,6 +1586,7 @@ void gemm_umma_launch_geometry(const GemmLaunch& g, int want_two_sm, int32_t out
     const int per = t.two_sm ? 2 : 1;
     int64_t units = g.num_sms / per;
     if (g.d.max_ctas > 0 && g.d.max_ctas / per >= 1 && g.d.max_ctas / per < units) units = g.d.max_ctas / per;
+    const bool one_round = n_tiles <= units;
     if (units > n_tiles) units = n_tiles;
     if (units < 1) units = 1;
     int smem = 0, stages = 0;
@@ -1596,7 +1598,7 @@ void gemm_umma_launch_geometry(const GemmLaunch& g, int want_two_sm, int32_t out
         else { smem = SmemPlan<false, 128>::kTotal; stages = SmemPlan<false, 128>::kStages; }
     }
     out[0] = (int32_t)(units * per); out[1] = 1; out[2] = 1;
-    out[3] = short_k_epilogue(g) ? kThreadsWide : kThreads; out[4] = 1; out[5] = 1;
+    out[3] = short_k_epilogue(g, one_round) ? kThreadsWide : kThreads; out[4] = 1; out[5] = 1;
     out[6] = smem;
     out[7] = stages;
 }
@@ -1722,8 +1724,10 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
     // 65536 x 8192 x 8192, which is why long K loops keep four warps and the TMA stores.
     {
         const Options& o = options();
+        const int per = two_sm ? 2 : 1;
+        const int64_t units_cap = (d.max_ctas > 0 && d.max_ctas / per >= 1 && d.max_ctas / per < units_est) ? d.max_ctas / per : units_est;
         const bool can = p.tma_store && g.n_extra_c == 0 && ((d.n * elem_size(d.c_type)) % 16) == 0;
-        if (can && (o.gemm_staged_store == 2 || (o.gemm_staged_store < 0 && short_k_epilogue(g)))) { p.lsu_stage = 1; p.tma_store = 0; }
+        if (can && (o.gemm_staged_store == 2 || (o.gemm_staged_store < 0 && short_k_epilogue(g, tiles_total <= units_cap)))) { p.lsu_stage = 1; p.tma_store = 0; }
         p.c_in = (p.lsu_stage && d.beta != 0.0f && (o.gemm_c_in >= 0 ? o.gemm_c_in : 1)) ? 1 : 0;
         p.epi_warps = (p.lsu_stage && o.gemm_epi_warps != 4) ? 2 * kEpiWarps : kEpiWarps;
     }
