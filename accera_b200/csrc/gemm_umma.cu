@@ -19,7 +19,7 @@
 // transposition) or, for 16-bit and 8-bit types, M / N-contiguous (column-major A, row-major B: "MN-major"
 // shared-memory descriptors), with 16-byte aligned rows.
 //
-// Kernel structure (one CTA per SM, 192 threads, or CTA pairs with cta_group::2):
+// Kernel structure (one CTA per SM, 192 or 320 threads, or CTA pairs with cta_group::2):
 //   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of a
 //               128-byte-wide K slab of A (128 rows) and B (256 rows, or 128 per CTA
 //               of a pair) into a ring of shared-memory stages (128B swizzle)
@@ -27,7 +27,8 @@
 //               K=32 bytes per instruction), commits to the stage's "empty"
 //               mbarrier, and after the last K slab to the accumulator's "full" one
 //   warps 2..5  epilogue: tcgen05.ld the 128 x 256 accumulator (each warp its own 32
-//               TMEM lanes, the next 32 columns in flight while these are worked on),
+//               TMEM lanes; launches with a short K loop run warps 2..9, two per lane
+//               quarter, each taking half of the columns),
 //               scale / add C / bias / ReLU / convert, then one of three ways out:
 //               shared-memory boxes stored by TMA (the default), boxes the warps move
 //               themselves with the old C copied in ahead of use (short K loops with
