@@ -36,6 +36,8 @@ def main() -> None:
     ap.add_argument("--compute", default="tensor_2sm")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--beta", type=float, default=1.0, help="GEMM cases: C <- A @ B + beta * C")
+    ap.add_argument("--a-col-major", action="store_true", help="gemm_bf16 / gemm_f16: A stored column-major (M contiguous)")
+    ap.add_argument("--b-row-major", action="store_true", help="gemm_bf16 / gemm_f16: B stored row-major (N contiguous)")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="a launch override for this run, e.g. gemm.group_n=16 (see accb_set_option)")
     a = ap.parse_args()
@@ -56,8 +58,8 @@ def main() -> None:
             C = torch.zeros(m, n, device=dev)
         else:
             dt = torch.bfloat16 if a.case == "gemm_bf16" else torch.float16
-            A = torch.randn(m, k, device=dev).to(dt)
-            B = (torch.randn(n, k, device=dev) / k ** 0.5).to(dt).t()
+            A = torch.randn(k, m, device=dev).to(dt).t() if a.a_col_major else torch.randn(m, k, device=dev).to(dt)
+            B = (torch.randn(k, n, device=dev) / k ** 0.5).to(dt) if a.b_row_major else (torch.randn(n, k, device=dev) / k ** 0.5).to(dt).t()
             C = torch.zeros(m, n, device=dev, dtype=dt if a.case == "gemm_bf16" else torch.float32)
         for _ in range(a.iters):
             rt.gemm(A, B, C, beta=a.beta, relu=a.case != "gemm_s8", compute=a.compute)
