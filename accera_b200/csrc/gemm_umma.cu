@@ -1140,6 +1140,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint32_t cin_issued = 0;                     // boxes whose copy has been issued (warp-uniform)
         int cin_t = unit, cin_box = 0;               // the tile and the box in it that is copied next
         int64_t cin_row0 = 0, cin_col_tile = 0;
+        const TC* cin_c = C;                         // C of the problem the copied tile belongs to
         auto cin_issue_upto = [&](uint32_t limit) {
             while (cin_issued < limit && cin_t < num_tiles) {
                 if (cin_box == 0) {
@@ -1147,6 +1148,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     tile_coords_batched(cin_t, p, problem, tm, tn);
                     cin_row0 = (int64_t)(tm * kCtas + (int)rank) * kBlockM + q * 32;
                     cin_col_tile = (int64_t)tn * BN;
+                    cin_c = C + (int64_t)problem * p.c_bs;
                 }
                 const int64_t box_col0 = cin_col_tile + (int64_t)(half * boxes_per_warp_tile + cin_box) * kBoxCols;
                 if (cin_row0 < p.m && box_col0 < p.n) {
@@ -1158,7 +1160,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         const int r = 4 * i + vr4;
                         uint8_t* dst = dst_box + r * 128 + ((vu ^ (r & 7)) << 4);
                         if (col_ok && cin_row0 + r < p.m)
-                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(C + (cin_row0 + r) * p.cs0 + col) : "memory");
+                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(cin_c + (cin_row0 + r) * p.cs0 + col) : "memory");
                         else
                             *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);    // outside the matrix: never stored
                     }
@@ -1235,7 +1237,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             const int r = 4 * i + vr4;
                             v[i] = *reinterpret_cast<const uint4*>(box + r * 128 + ((vu ^ (r & 7)) << 4));
                         }
-                        TC* dst = C + (row0 + vr4) * p.cs0 + col;
+                        TC* dst = C + (int64_t)problem * p.c_bs + (row0 + vr4) * p.cs0 + col;
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
                             if (col_ok && row0 + 4 * i + vr4 < p.m) *reinterpret_cast<uint4*>(dst + (int64_t)(4 * i) * p.cs0) = v[i];
@@ -1428,7 +1430,8 @@ bool short_k_epilogue(const GemmLaunch& g, bool one_round)
     const int64_t slabs = (d.k * elem_size(d.a_type) + kSlabBytes - 1) / kSlabBytes;
     const bool c_ok = d.c_stride[1] == 1 && (d.c_stride[0] * elem_size(d.c_type)) % 16 == 0 &&
                       (reinterpret_cast<uintptr_t>(g.c) & 15) == 0 && ((d.n * elem_size(d.c_type)) % 16) == 0;
-    return c_ok && g.batch <= 1 && g.n_extra_c == 0 && (slabs <= 32 || (one_round && slabs <= 64));
+    const bool batch_ok = g.batch <= 1 || (g.c_batch_stride * elem_size(d.c_type)) % 16 == 0;
+    return c_ok && batch_ok && g.n_extra_c == 0 && (slabs <= 32 || (one_round && slabs <= 64));
 }
 
 uint32_t make_idesc(int a_type, int b_type, bool int_acc, bool f16_out_acc, int m, int n, bool a_mn = false, bool b_mn = false)
@@ -1727,8 +1730,11 @@ int launch_gemm_umma(const GemmLaunch& g, int want_two_sm, const char** err)
         const Options& o = options();
         const int per = two_sm ? 2 : 1;
         const int64_t units_cap = (d.max_ctas > 0 && d.max_ctas / per >= 1 && d.max_ctas / per < units_est) ? d.max_ctas / per : units_est;
-        const bool can = p.tma_store && g.n_extra_c == 0 && ((d.n * elem_size(d.c_type)) % 16) == 0;
-        if (can && (o.gemm_staged_store == 2 || (o.gemm_staged_store < 0 && short_k_epilogue(g, tiles_total <= units_cap)))) { p.lsu_stage = 1; p.tma_store = 0; }
+        // (the warps address C themselves, so unlike the TMA-stored boxes this path also serves batched launches)
+        const bool batch_ok = batch == 1 || (g.c_batch_stride * elem_size(d.c_type)) % 16 == 0;
+        const bool can = c_tma_storable(d, g.c) && batch_ok && g.n_extra_c == 0 && ((d.n * elem_size(d.c_type)) % 16) == 0 &&
+                         !(o.gemm_staged_store == 0 || o.gemm_staged_store == 1);
+        if (can && (o.gemm_staged_store == 2 || short_k_epilogue(g, tiles_total <= units_cap))) { p.lsu_stage = 1; p.tma_store = 0; }
         p.c_in = (p.lsu_stage && d.beta != 0.0f && (o.gemm_c_in >= 0 ? o.gemm_c_in : 1)) ? 1 : 0;
         p.epi_warps = (p.lsu_stage && o.gemm_epi_warps != 4) ? 2 * kEpiWarps : kEpiWarps;
     }
