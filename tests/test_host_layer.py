@@ -770,3 +770,24 @@ def test_options_are_validated_and_reset():
         with pytest.raises(runtime.AccbError):
             runtime.set_option(name, value)
     assert runtime.selected_device() == -1
+
+
+def test_launch_geometry_follows_the_epilogue_the_launch_will_use():
+    """accb_gemm_launch_geometry reports the block the launch code really uses: 320 threads (eight epilogue warps) where
+    the K loop is short enough for the epilogue to show - up to 32 slabs of 128 bytes, or 64 when every CTA has one
+    tile - and 192 otherwise."""
+    runtime.set_option("reset", 0)
+    g = runtime.gemm_launch_geometry
+    assert g(1024, 1024, 1024)["block"] == [320, 1, 1]             # 16 slabs
+    assert g(4096, 4096, 2048)["block"] == [320, 1, 1]             # 32 slabs, several tiles per CTA
+    assert g(4096, 4096, 4096)["block"] == [192, 1, 1]             # 64 slabs, 3.5 rounds of tiles
+    assert g(1024, 4096, 4096)["block"] == [320, 1, 1]             # 64 slabs, one tile per CTA pair
+    assert g(65536, 8192, 8192)["block"] == [192, 1, 1]            # the benchmark's launch
+    assert g(8192, 8192, 8192, in_type="int8")["block"] == [192, 1, 1]     # 64 slabs of 128 int8, 14 rounds
+    assert g(2048, 2048, 2048, in_type="int8")["block"] == [320, 1, 1]     # 16 slabs
+    assert g(1024, 1000, 1024)["block"] == [320, 1, 1]             # rows of 2000 bytes end on a 16-byte boundary
+    assert g(1024, 1004, 1024)["block"] == [192, 1, 1]             # rows of 2008 bytes do not: TMA-stored boxes
+    for name, value in (("gemm.epi_warps", 4), ("gemm.epi_warps", 8), ("gemm.split_k", 0), ("gemm.split_k", 4), ("gemm.c_in", 0),
+                        ("gemm.staged_store", 2), ("stream_kernels.pdl", 0)):
+        runtime.set_option(name, value)                              # accepted
+    runtime.set_option("reset", 0)
