@@ -23,7 +23,7 @@ repack_rows_kernel(const uint8_t* __restrict__ src, int64_t src_pitch, int64_t r
     const int64_t total = dst_rows * vec_per_row;
     for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = v / vec_per_row, c0 = (v - r * vec_per_row) * kPer;
-        T e[kPer];
+        alignas(16) T e[kPer];
         const T* s = reinterpret_cast<const T*>(src + r * src_pitch);
 #pragma unroll
         for (int i = 0; i < kPer; ++i) e[i] = (r < rows && c0 + i < width) ? s[c0 + i] : T(0);
